@@ -10,8 +10,13 @@ its caches by attention layers only and its state buffers by the other layers
 `[slot, ...]` tensor per schedule entry that asks for one (with one more row at the end, where the padding
 rows of fixed-size launches land); the Llama decoder asks for none.
 
-Storage of a group: K and V, each `[entry, page, kv_head, PAGE_TOKENS, head_dim]`.  One page of
-one kv head is a contiguous block, which is what the decode kernel streams.
+Storage of a group: K and V, each `[entry, page, kv_head, PAGE_TOKENS, head_dim]` (V with `v_head_dim` in
+place of `head_dim` where a mixer's values are not as wide as its keys).  One page of one kv head is a
+contiguous block, which is what the decode kernel streams.
+
+Kinds of request: "full" keeps every position; "window" only the last `window` positions; "chunk" only the
+positions of the chunk of `window` positions (counted from position 0) that the sequence's newest token lies in.
+The last two give pages back as the sequence moves on.
 """
 from __future__ import annotations
 
@@ -27,17 +32,26 @@ from .pages import PAGE_TOKENS, CacheFullError, PagePool, SlotAllocator, pages_f
 @dataclass(frozen=True)
 class CacheRequest:
     """What a mixer wants kept per token.  kind "full": every position stays visible;
-    kind "window": only the last `window` positions are ever read again."""
+    kind "window": only the last `window` positions are ever read again; kind "chunk": only positions p with
+    floor(p / window) equal to that of the reader's own position.  `v_head_dim`: the values' width when it is not
+    the keys' `head_dim`."""
     kind: str
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    v_head_dim: Optional[int] = None
 
     def __post_init__(self):
-        if self.kind not in ("full", "window"):
+        if self.kind not in ("full", "window", "chunk"):
             raise ValueError(f"unknown cache kind {self.kind!r}")
-        if self.kind == "window" and (self.window is None or self.window < 1):
-            raise ValueError("a window cache needs a positive window")
+        if self.kind in ("window", "chunk") and (self.window is None or self.window < 1):
+            raise ValueError(f"a {self.kind} cache needs a positive size")
+        if self.v_head_dim is not None and self.v_head_dim < 1:
+            raise ValueError("the values' width must be positive")
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_head_dim is None else self.v_head_dim
 
 
 @dataclass(frozen=True)
@@ -56,6 +70,7 @@ class LayerMemory:
     window: Optional[int]
     writes: bool                          # False when the entry reads another entry's memory
     state: Optional[torch.Tensor]         # [max_slots + 1, *shape] or None; the last row (slot -1) is for padding rows
+    chunk: Optional[int] = None           # size of the chunks of a "chunk" group
 
 
 class _Group:
@@ -81,7 +96,7 @@ class _Group:
         # zero-filled once: rows past a sequence's length are never read, but the padding rows of
         # fixed-size launches read the trash page, which must hold finite numbers
         self.k = torch.zeros(shape, dtype=self.dtype, device=self.device)
-        self.v = torch.zeros(shape, dtype=self.dtype, device=self.device)
+        self.v = torch.zeros(shape[:-1] + (r.value_dim,), dtype=self.dtype, device=self.device)
         self.table_dev = torch.zeros(self.table_host.shape, dtype=torch.int32, device=self.device)
 
 
@@ -133,7 +148,7 @@ class SequenceCache:
         total = 0
         esz = torch.empty((), dtype=self.dtype).element_size()
         for g in self._groups:
-            total += 2 * len(g.entries) * g.request.num_kv_heads * g.request.head_dim * esz
+            total += len(g.entries) * g.request.num_kv_heads * (g.request.head_dim + g.request.value_dim) * esz
         return total
 
     def state_bytes_per_sequence(self) -> int:
@@ -197,13 +212,18 @@ class SequenceCache:
                     g.dirty[s] = (min(lo, have), max(hi, have + more))
 
     def commit(self, slot: int, new_len: int) -> None:
-        """The slot now holds `new_len` tokens.  Window groups give back pages no later query can see."""
+        """The slot now holds `new_len` tokens.  Window and chunk groups give back pages no later query can see."""
         self.lengths[slot] = new_len
         for g in self._groups:
-            if g.request.kind != "window":
+            if g.request.kind == "window":
+                # a query at position p >= new_len reads keys > p - window >= new_len - window
+                dead_before = max(0, new_len - g.request.window + 1) // PAGE_TOKENS
+            elif g.request.kind == "chunk":
+                # a query at position p >= new_len reads keys from the start of its own chunk, at or after the start
+                # of the chunk that position new_len lies in
+                dead_before = ((new_len // g.request.window) * g.request.window) // PAGE_TOKENS
+            else:
                 continue
-            # a query at position p >= new_len reads keys > p - window >= new_len - window
-            dead_before = max(0, new_len - g.request.window + 1) // PAGE_TOKENS
             first = g.first_live[slot]
             if dead_before > first:
                 pages = g.pages[slot]
@@ -235,7 +255,7 @@ class SequenceCache:
         cur = self.lengths[slot]
         if pos >= cur:
             return cur
-        if self._state or any(g.request.kind == "window" and g.first_live[slot] * PAGE_TOKENS > 0 for g in self._groups):
+        if self._state or any(g.request.kind in ("window", "chunk") and g.first_live[slot] * PAGE_TOKENS > 0 for g in self._groups):
             return cur
         for g in self._groups:
             keep = pages_for(pos)
@@ -287,4 +307,4 @@ class SequenceCache:
             return LayerMemory(None, None, None, None, writes, state)
         g, idx = gi
         return LayerMemory(g.k[idx], g.v[idx], g.table_dev, g.request.window if g.request.kind == "window" else None,
-                           writes, state)
+                           writes, state, g.request.window if g.request.kind == "chunk" else None)

@@ -66,9 +66,13 @@ def read_config_json(model_dir: str) -> Dict[str, Any]:
 
 
 def architecture_of(raw: Mapping[str, Any]) -> str:
+    """The name config.json gives its model: the first of `architectures`, or the string `architecture`."""
+    one = raw.get("architecture")
+    if isinstance(one, str) and one and "architectures" not in raw:
+        return one
     archs = raw.get("architectures")
     if not isinstance(archs, (list, tuple)) or not archs or not isinstance(archs[0], str):
-        raise ConfigError("config.json: \"architectures\" must be a non-empty list of names")
+        raise ConfigError("config.json: \"architectures\" must be a non-empty list of names (or \"architecture\" one name)")
     return archs[0]
 
 

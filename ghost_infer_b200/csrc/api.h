@@ -184,6 +184,83 @@ int gi_attn_decode_generic(void* out, long ldo, float* part_o, float* part_ml, c
                            const void* kcache, const void* vcache, const int* block_table, int max_pages,
                            const int* seq_slots, const int* seq_lens, int n_seqs, int n_heads, int n_kv, int hd,
                            float scale, int window, int n_splits, int own_tiles, void* stream);
+
+// The same two operations with what a model's attention may add, each off at its neutral value: values of another
+// width than the keys (hdv; the value cache is [page][kv head][64][hdv], the output [tokens, heads * hdv]), a cap
+// on the scores (s <- cap * tanh(s / cap); 0: none), a sink per head (float[heads]: one more term exp(sink) in the
+// softmax's denominator, without key or value; null: none) and chunks (a query sees keys of its own chunk
+// floor(pos / chunk) only; 0: none).  part_o holds hdv values per (sequence, head, slice).
+int gi_attn_prefill_generic_ex(void* out, long ldo, const void* q, long ldq, int dtype, const void* kcache,
+                               const void* vcache, const int* block_table, int max_pages, const int* cu_seqlens,
+                               const int* seq_slots, const int* seq_pos0, int n_seqs, int max_q_len, int n_heads,
+                               int n_kv, int hd, float scale, int window, int hdv, float softcap, const float* sinks,
+                               int chunk, void* stream);
+int gi_attn_decode_generic_ex(void* out, long ldo, float* part_o, float* part_ml, const void* q, long ldq, int dtype,
+                              const void* kcache, const void* vcache, const int* block_table, int max_pages,
+                              const int* seq_slots, const int* seq_lens, int n_seqs, int n_heads, int n_kv, int hd,
+                              float scale, int window, int n_splits, int own_tiles, int hdv, float softcap,
+                              const float* sinks, int chunk, void* stream);
+
+// Keys and values of a step's tokens into the cache without rotation, for packed rows [q: heads * hd | k: kv * hd |
+// v: kv * hdv].  `first` (optional, [tokens, kv * hdv], the rows' type): the values are first blended with it,
+// v <- (1 - lambda) v + lambda first, in 32-bit, lambda read from device memory; the blended values are also
+// written back into the rows.  `copy_to` (optional, same shape): receives the rows' values as they are (for a later
+// layer's `first`).
+int gi_kv_store(void* qkv, int dtype, long ld, const void* first, const float* lambda, void* copy_to,
+                const int* positions, const int* slots, const int* block_table, int max_pages, void* kcache,
+                void* vcache, int n_tokens, int n_heads, int n_kv, int hd, int hdv, int write_cache, void* stream);
+
+// ---- Mamba-2 (state-space duality) mixer.  Per-sequence state rows live in one float matrix [rows, row_floats]:
+// first heads * N * P floats of S (per head N x P), then channels * (taps - 1) floats of the convolution's last
+// inputs (oldest first per channel).  A sequence of slot s uses row s; slot -1 (a padding row) uses the last row.
+// proj: the input projection's rows [tokens, 2 * inner + 2 * G * N + heads] = [z | x | B | C | dt], inner = heads * P.
+// conv: xbc_out[t, c] = silu(bias[c] + sum_j w[c, j] * in[t - (taps - 1) + j, c]) over channels c of [x | B | C], inputs
+// before the step's first token from the state (zero for a fresh sequence); then the state takes the last taps - 1
+// inputs (gi_mamba2_conv_update, a launch of its own because it overwrites what the first reads).
+int gi_mamba2_conv(void* xbc_out, const void* proj, int dtype, long ld_proj, const void* conv_w, const void* conv_b,
+                   int w_dtype, const float* state, long state_ld, int state_rows, const int* cu_seqlens,
+                   const int* seq_slots, int n_seqs, int max_q_len, int inner, int channels, int taps, int s_floats,
+                   void* stream);
+int gi_mamba2_conv_update(const void* proj, int dtype, long ld_proj, float* state, long state_ld, int state_rows,
+                          const int* cu_seqlens, const int* seq_slots, int n_seqs, int inner, int channels, int taps,
+                          int s_floats, void* stream);
+// scan: dt <- softplus(dt + dt_bias); per head S <- exp(-exp(A_log) dt) S + dt B x^T, y = S^T C + D x, everything in
+// 32-bit, tokens of a sequence in order, S read from and written back to the state.  y: float [tokens, inner].
+int gi_mamba2_scan(float* y, const void* xbc, const void* proj, int dtype, long ld_proj, const void* dt_bias,
+                   const void* a_log, const void* d_skip, int w_dtype, float* state, long state_ld, int state_rows,
+                   const int* cu_seqlens, const int* seq_slots, int n_seqs, int heads, int P, int N, int groups,
+                   void* stream);
+// out[t, :] = groupwise_rmsnorm(y[t, :] * silu(z[t, :])) * w, z the first inner columns of proj; `parts` equal parts,
+// each divided by its own root mean square (eps inside the root).
+int gi_mamba2_gate_norm(void* out, int out_dtype, const float* y, const void* proj, int dtype, long ld_proj,
+                        const void* w, int w_dtype, int n_tokens, int inner, int parts, float eps, void* stream);
+
+// ---- routed feed-forward (mixture of experts).
+// route: logits = h W_r^T in 32-bit; the `top` largest per token (first wins a tie), weights = softmax over the chosen
+// logits; optional shared gate sg[t] = sigmoid(h . w_sg).  ids int[tokens, top], wts float[tokens, top].
+int gi_moe_route(int* ids, float* wts, float* sgate, const void* h, int dtype, long ldh, const void* w_router,
+                 const void* w_sg, int w_dtype, int n_tokens, int width, int experts, int top, void* stream);
+// plan: a stable counting sort of the tokens' choices by expert.  offsets int[experts + 1]; perm int[entries] (sorted
+// place -> entry t * top + k); inv int[entries] (entry -> sorted place).  scratch: int[(entries + 1023) / 1024 *
+// experts * 2 + entries].
+int gi_moe_plan(int* offsets, int* perm, int* inv, int* scratch, const int* ids, int entries, int experts, void* stream);
+// Products over the sorted rows, each row with its expert's matrix (w + expert * w_stride, [n, k] row-major).
+// gate_up: out[r, 0..f) = silu(a[src(r)] Wg^T) * (a[src(r)] Wu^T), W = [gate (f rows); up (f rows)], src(r) = perm[r] / top.
+// down: out[r, :] = a[r] W^T stored as float.
+int gi_moe_gemm_gate_up(void* out, int dtype, const void* a, long lda, const void* w, int w_dtype, long w_stride,
+                        const int* offsets, const int* perm, int entries, int top, int experts, int f, int k,
+                        void* stream);
+int gi_moe_gemm_down(float* out, const void* a, int dtype, long lda, const void* w, int w_dtype, long w_stride,
+                     const int* offsets, int entries, int experts, int n, int k, void* stream);
+// residual[t, :] += sum_k wts[t, k] * down[inv[t * top + k], :] (k in order) + sgate[t] * shared[t, :] (if given).
+int gi_moe_combine(float* residual, const float* down, const int* inv, const float* wts, const float* shared,
+                   const float* sgate, int n_tokens, int width, int top, void* stream);
+
+// act(gate) * up over rows [gate | up] (or blocks [8 gate | 8 up]); act 0: silu, 1: the tanh form of gelu.
+int gi_act_mul(void* out, const void* gate_up, int dtype, int n_rows, int f, int interleaved, int act, void* stream);
+// x[t, :] = table[tokens[t], :] * scale.
+int gi_embed_scaled(float* out, const void* table, int table_dtype, const int* tokens, int n_tokens, int d, int vocab,
+                    float scale, void* stream);
 // own_tiles > 0: slice s of a sequence holds tiles [s * own_tiles, (s + 1) * own_tiles) of 32 keys of its own span,
 // whatever n_splits is (which must cover the longest span); 0: each span is cut into n_splits equal slices.
 

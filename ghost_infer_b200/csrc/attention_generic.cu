@@ -8,7 +8,12 @@
 //  * decode: a block takes one kv head of one sequence and one slice of its context, every query
 //    head of the group sharing each key/value row it reads; slices are merged by a second kernel
 //    (the roles of attention_partial_gqa and attention_combine, src/cuda.rs:1684-1865, :2806-2839).
-// Keys and values live in pages of 64 positions: [page][kv head][64][hd].
+// Keys and values live in pages of 64 positions: keys [page][kv head][64][hd], values [page][kv head][64][hdv]
+// (hdv = hd unless a model's values are narrower or wider than its keys).
+// Options that a model's attention may name, each off at its neutral value: a cap on the scores
+// (s <- cap * tanh(s / cap), cap > 0), a learned sink per head (a term exp(sink_h) in the softmax's denominator that
+// has no key and no value: sinks != null), and chunks of positions (a query sees only keys of its own chunk
+// floor(pos / chunk), counted from position 0 of the sequence: chunk > 0).
 #include <math.h>
 
 #include "api.h"
@@ -25,13 +30,14 @@ __global__ void __launch_bounds__(128)
 attn_prefill_kernel(T* __restrict__ out, long ldo, const T* __restrict__ q, long ldq, const T* __restrict__ kcache,
                     const T* __restrict__ vcache, const int* __restrict__ block_table, int max_pages,
                     const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slots,
-                    const int* __restrict__ seq_pos0, int n_heads, int n_kv, int hd, float scale, int window) {
+                    const int* __restrict__ seq_pos0, int n_heads, int n_kv, int hd, float scale, int window,
+                    int hdv, float softcap, const float* __restrict__ sinks, int chunk) {
   extern __shared__ float smem[];
-  const int ldk = hd + 1;
+  const int ldk = hd + 1, ldv = hdv + 1;
   float* Qs = smem;                  // [QT][hd+1]
   float* Ks = Qs + QT * ldk;         // [KT][hd+1]
-  float* Vs = Ks + KT * ldk;         // [KT][hd+1]
-  float* Ps = Vs + KT * ldk;         // [QT][KT+1]
+  float* Vs = Ks + KT * ldk;         // [KT][hdv+1]
+  float* Ps = Vs + KT * ldv;         // [QT][KT+1]
 
   const int b = blockIdx.z, h = blockIdx.y;
   const int tok0 = cu_seqlens[b], qlen = cu_seqlens[b + 1] - tok0;
@@ -51,7 +57,9 @@ attn_prefill_kernel(T* __restrict__ out, long ldo, const T* __restrict__ q, long
   const int p_last = pos0 + q0 + rows_here - 1;    // the block's last position
   int t_first = 0;                                 // the first key any row of this block may see
   if (window > 0) t_first = max(0, pos0 + q0 - window + 1);
+  if (chunk > 0) t_first = max(t_first, ((pos0 + q0) / chunk) * chunk);
   const int t_begin = (t_first / KT) * KT;
+  const int c_row = chunk > 0 ? p_row / chunk : 0;
 
   float m = -INFINITY, l = 0.f;
   float acc[DPT];
@@ -61,12 +69,20 @@ attn_prefill_kernel(T* __restrict__ out, long ldo, const T* __restrict__ q, long
   for (int kt = t_begin; kt <= p_last; kt += KT) {
     __syncthreads();
     const int page = block_table[(size_t)slot * max_pages + kt / PAGE_TOKENS];
-    const size_t base = (((size_t)page * n_kv + kvh) * PAGE_TOKENS + (kt % PAGE_TOKENS)) * hd;
+    const size_t row0 = ((size_t)page * n_kv + kvh) * PAGE_TOKENS + (kt % PAGE_TOKENS);
+    const size_t base = row0 * hd, base_v = row0 * hdv;
     for (int idx = tid; idx < KT * hd; idx += 128) {
       const int j = idx / hd, d = idx % hd;
       const bool live = kt + j <= p_last && kt + j >= t_first;   // rows no query here sees are not read
       Ks[j * ldk + d] = live ? gi::ldf(kcache + base + (size_t)j * hd + d) : 0.f;
-      Vs[j * ldk + d] = live ? gi::ldf(vcache + base + (size_t)j * hd + d) : 0.f;
+      if (hdv == hd) Vs[j * ldv + d] = live ? gi::ldf(vcache + base_v + (size_t)j * hdv + d) : 0.f;
+    }
+    if (hdv != hd) {
+      for (int idx = tid; idx < KT * hdv; idx += 128) {
+        const int j = idx / hdv, d = idx % hdv;
+        const bool live = kt + j <= p_last && kt + j >= t_first;
+        Vs[j * ldv + d] = live ? gi::ldf(vcache + base_v + (size_t)j * hdv + d) : 0.f;
+      }
     }
     __syncthreads();
     float s[8];
@@ -79,8 +95,10 @@ attn_prefill_kernel(T* __restrict__ out, long ldo, const T* __restrict__ q, long
       const float* qr = Qs + row * ldk;
       const float* kr = Ks + j * ldk;
       for (int d = 0; d < hd; ++d) dot = fmaf(qr[d], kr[d], dot);
-      const bool ok = row_ok && t <= p_row && (window <= 0 || t > p_row - window);
-      s[jj] = ok ? dot * scale : -INFINITY;
+      const bool ok = row_ok && t <= p_row && (window <= 0 || t > p_row - window) && (chunk <= 0 || t / chunk == c_row);
+      float sc = dot * scale;
+      if (softcap > 0.f) sc = softcap * tanhf(sc / softcap);
+      s[jj] = ok ? sc : -INFINITY;
       tile_max = fmaxf(tile_max, s[jj]);
     }
     tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 1));
@@ -108,22 +126,31 @@ attn_prefill_kernel(T* __restrict__ out, long ldo, const T* __restrict__ q, long
     for (int i = 0; i < DPT; ++i) acc[i] *= alpha;
     for (int j = 0; j < KT; ++j) {
       const float p = Ps[row * (KT + 1) + j];
-      const float* vr = Vs + j * ldk;
+      const float* vr = Vs + j * ldv;
 #pragma unroll
       for (int i = 0; i < DPT; ++i) {
         const int d = sub + 4 * i;
-        if (d < hd) acc[i] = fmaf(p, vr[d], acc[i]);
+        if (d < hdv) acc[i] = fmaf(p, vr[d], acc[i]);
       }
     }
     __syncwarp();
   }
   if (row_ok) {
+    if (sinks != nullptr) {
+      // the sink: one more term of the denominator, with no value behind it
+      const float sk = sinks[h];
+      const float m_f = fmaxf(m, sk);
+      const float a = (m == -INFINITY) ? 0.f : expf(m - m_f);
+      l = l * a + expf(sk - m_f);
+#pragma unroll
+      for (int i = 0; i < DPT; ++i) acc[i] *= a;
+    }
     const float inv = l > 0.f ? 1.0f / l : 0.f;
-    T* o = out + (size_t)(tok0 + q0 + row) * ldo + (size_t)h * hd;
+    T* o = out + (size_t)(tok0 + q0 + row) * ldo + (size_t)h * hdv;
 #pragma unroll
     for (int i = 0; i < DPT; ++i) {
       const int d = sub + 4 * i;
-      if (d < hd) gi::stf(o + d, acc[i] * inv);
+      if (d < hdv) gi::stf(o + d, acc[i] * inv);
     }
   }
 }
@@ -137,11 +164,11 @@ attn_decode_kernel(T* __restrict__ out, long ldo, float* __restrict__ part_o, fl
                    const T* __restrict__ q, long ldq, const T* __restrict__ kcache, const T* __restrict__ vcache,
                    const int* __restrict__ block_table, int max_pages, const int* __restrict__ seq_slots,
                    const int* __restrict__ seq_lens, int n_heads, int n_kv, int hd, float scale, int window,
-                   int n_splits, int own_tiles) {
+                   int n_splits, int own_tiles, int hdv, float softcap, const float* __restrict__ sinks, int pos_chunk) {
   extern __shared__ float smem[];
   float* Qs = smem;                       // [GC][hd]
-  float* Mo = Qs + GC * hd;               // [4][GC][hd] warp outputs
-  float* Mm = Mo + 4 * GC * hd;           // [4][GC] warp maxima
+  float* Mo = Qs + GC * hd;               // [4][GC][hdv] warp outputs
+  float* Mm = Mo + 4 * GC * hdv;          // [4][GC] warp maxima
   float* Ml = Mm + 4 * GC;                // [4][GC] warp sums
 
   const int group = n_heads / n_kv;
@@ -161,6 +188,7 @@ attn_decode_kernel(T* __restrict__ out, long ldo, float* __restrict__ part_o, fl
 
   int t_first = 0;
   if (window > 0) t_first = max(0, len - window);
+  if (pos_chunk > 0) t_first = max(t_first, ((len - 1) / pos_chunk) * pos_chunk);
   const int t_base = (t_first / KT) * KT;
   const int tiles = len > t_base ? (len - t_base + KT - 1) / KT : 0;
   // own_tiles > 0: a slice is that many tiles of the sequence's own span, so its sums do not depend on what else
@@ -180,7 +208,8 @@ attn_decode_kernel(T* __restrict__ out, long ldo, float* __restrict__ part_o, fl
   for (int tile = tile_lo + warp; tile < tile_hi; tile += 4) {
     const int t0 = t_base + tile * KT;
     const int page = slot >= 0 ? block_table[(size_t)slot * max_pages + t0 / PAGE_TOKENS] : 0;
-    const size_t base = (((size_t)page * n_kv + kvh) * PAGE_TOKENS + (t0 % PAGE_TOKENS)) * hd;
+    const size_t row0 = ((size_t)page * n_kv + kvh) * PAGE_TOKENS + (t0 % PAGE_TOKENS);
+    const size_t base = row0 * hd, base_v = row0 * hdv;
     const int t = t0 + lane;
     const bool ok = t < len && t >= t_first;
     float s[GC];
@@ -197,7 +226,9 @@ attn_decode_kernel(T* __restrict__ out, long ldo, float* __restrict__ part_o, fl
     float p[GC];
 #pragma unroll
     for (int g = 0; g < GC; ++g) {
-      const float sc = ok ? s[g] * scale : -INFINITY;
+      float sc = s[g] * scale;
+      if (softcap > 0.f) sc = softcap * tanhf(sc / softcap);
+      if (!ok) sc = -INFINITY;
       const float tmax = gi::warp_max(sc);
       const float m_new = fmaxf(m[g], tmax);      // finite: a tile always holds at least one live key
       const float alpha = (m[g] == -INFINITY) ? 0.f : expf(m[g] - m_new);
@@ -213,7 +244,7 @@ attn_decode_kernel(T* __restrict__ out, long ldo, float* __restrict__ part_o, fl
 #pragma unroll
       for (int c = 0; c < DC; ++c) {
         const int d = lane + 32 * c;
-        v[c] = (d < hd && t0 + j >= t_first) ? gi::ldf(vcache + base + (size_t)j * hd + d) : 0.f;
+        v[c] = (d < hdv && t0 + j >= t_first) ? gi::ldf(vcache + base_v + (size_t)j * hdv + d) : 0.f;
       }
 #pragma unroll
       for (int g = 0; g < GC; ++g) {
@@ -234,12 +265,12 @@ attn_decode_kernel(T* __restrict__ out, long ldo, float* __restrict__ part_o, fl
 #pragma unroll
     for (int c = 0; c < DC; ++c) {
       const int d = lane + 32 * c;
-      if (d < hd) Mo[(warp * GC + g) * hd + d] = o[g][c];
+      if (d < hdv) Mo[(warp * GC + g) * hdv + d] = o[g][c];
     }
   }
   __syncthreads();
-  for (int idx = tid; idx < gcount * hd; idx += 128) {
-    const int g = idx / hd, d = idx % hd;
+  for (int idx = tid; idx < gcount * hdv; idx += 128) {
+    const int g = idx / hdv, d = idx % hdv;
     float mm = -INFINITY;
     for (int w = 0; w < 4; ++w) mm = fmaxf(mm, Mm[w * GC + g]);
     float tot = 0.f, val = 0.f;
@@ -249,15 +280,24 @@ attn_decode_kernel(T* __restrict__ out, long ldo, float* __restrict__ part_o, fl
         if (mw == -INFINITY) continue;
         const float wgt = expf(mw - mm);
         tot += Ml[w * GC + g] * wgt;
-        val += Mo[(w * GC + g) * hd + d] * wgt;
+        val += Mo[(w * GC + g) * hdv + d] * wgt;
       }
     }
     const int h = h0 + g;
+    if (sinks != nullptr && sp == 0) {
+      // the sink counts once per (sequence, head): the first slice takes it in, as one more term without a value
+      const float sk = sinks[h];
+      const float m_f = fmaxf(mm, sk);
+      const float a = (mm == -INFINITY) ? 0.f : expf(mm - m_f);
+      tot = tot * a + expf(sk - m_f);
+      val *= a;
+      mm = m_f;
+    }
     if (n_splits == 1) {
-      gi::stf(out + (size_t)b * ldo + (size_t)h * hd + d, tot > 0.f ? val / tot : 0.f);
+      gi::stf(out + (size_t)b * ldo + (size_t)h * hdv + d, tot > 0.f ? val / tot : 0.f);
     } else {
       const size_t pi = ((size_t)b * n_heads + h) * n_splits + sp;
-      part_o[pi * hd + d] = val;
+      part_o[pi * hdv + d] = val;
       if (d == 0) {
         part_ml[pi * 2] = mm;
         part_ml[pi * 2 + 1] = tot;
@@ -340,7 +380,8 @@ __global__ void attn_combine_kernel(T* __restrict__ out, long ldo, const float* 
 template <typename T>
 int launch_prefill(int dpt, dim3 grid, size_t smem, cudaStream_t s, T* out, long ldo, const T* q, long ldq,
                    const T* kc, const T* vc, const int* bt, int max_pages, const int* cu, const int* slots,
-                   const int* pos0, int H, int KV, int hd, float scale, int window) {
+                   const int* pos0, int H, int KV, int hd, float scale, int window, int hdv, float softcap,
+                   const float* sinks, int chunk) {
 #define GI_PREFILL_CASE(D)                                                                                       \
   case D: {                                                                                                      \
     auto kern = attn_prefill_kernel<T, D>;                                                                       \
@@ -348,7 +389,7 @@ int launch_prefill(int dpt, dim3 grid, size_t smem, cudaStream_t s, T* out, long
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
       if (e != cudaSuccess) return gi::fail(GI_ERR_CUDA, "attention prefill: %s", cudaGetErrorString(e));        \
     }                                                                                                            \
-    kern<<<grid, 128, smem, s>>>(out, ldo, q, ldq, kc, vc, bt, max_pages, cu, slots, pos0, H, KV, hd, scale, window); \
+    kern<<<grid, 128, smem, s>>>(out, ldo, q, ldq, kc, vc, bt, max_pages, cu, slots, pos0, H, KV, hd, scale, window, hdv, softcap, sinks, chunk); \
     break;                                                                                                       \
   }
   switch (dpt) {
@@ -367,7 +408,8 @@ int launch_prefill(int dpt, dim3 grid, size_t smem, cudaStream_t s, T* out, long
 template <typename T, int GC>
 int launch_decode_dc(int dc, dim3 grid, size_t smem, cudaStream_t s, T* out, long ldo, float* po, float* pml,
                      const T* q, long ldq, const T* kc, const T* vc, const int* bt, int max_pages, const int* slots,
-                     const int* lens, int H, int KV, int hd, float scale, int window, int n_splits, int own_tiles) {
+                     const int* lens, int H, int KV, int hd, float scale, int window, int n_splits, int own_tiles,
+                     int hdv, float softcap, const float* sinks, int chunk) {
 #define GI_DECODE_CASE(D)                                                                                        \
   case D: {                                                                                                      \
     auto kern = attn_decode_kernel<T, GC, D>;                                                                    \
@@ -375,7 +417,7 @@ int launch_decode_dc(int dc, dim3 grid, size_t smem, cudaStream_t s, T* out, lon
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
       if (e != cudaSuccess) return gi::fail(GI_ERR_CUDA, "attention decode: %s", cudaGetErrorString(e));         \
     }                                                                                                            \
-    kern<<<grid, 128, smem, s>>>(out, ldo, po, pml, q, ldq, kc, vc, bt, max_pages, slots, lens, H, KV, hd, scale, window, n_splits, own_tiles); \
+    kern<<<grid, 128, smem, s>>>(out, ldo, po, pml, q, ldq, kc, vc, bt, max_pages, slots, lens, H, KV, hd, scale, window, n_splits, own_tiles, hdv, softcap, sinks, chunk); \
     break;                                                                                                       \
   }
   switch (dc) {
@@ -412,18 +454,29 @@ extern "C" int gi_attn_prefill_generic(void* out, long ldo, const void* q, long 
                                        const int* cu_seqlens, const int* seq_slots, const int* seq_pos0, int n_seqs,
                                        int max_q_len, int n_heads, int n_kv, int hd, float scale, int window,
                                        void* stream) {
+  return gi_attn_prefill_generic_ex(out, ldo, q, ldq, dtype, kcache, vcache, block_table, max_pages, cu_seqlens, seq_slots,
+                                    seq_pos0, n_seqs, max_q_len, n_heads, n_kv, hd, scale, window, hd, 0.f, nullptr, 0, stream);
+}
+
+extern "C" int gi_attn_prefill_generic_ex(void* out, long ldo, const void* q, long ldq, int dtype, const void* kcache,
+                                          const void* vcache, const int* block_table, int max_pages,
+                                          const int* cu_seqlens, const int* seq_slots, const int* seq_pos0, int n_seqs,
+                                          int max_q_len, int n_heads, int n_kv, int hd, float scale, int window,
+                                          int hdv, float softcap, const float* sinks, int chunk, void* stream) {
   if (n_seqs <= 0 || max_q_len <= 0) return GI_OK;
+  if (hdv <= 0 || hdv > 256) return gi::fail(GI_ERR_UNSUPPORTED, "attention: value size %d is outside 1..256", hdv);
+  if (chunk < 0 || softcap < 0.f) return gi::fail(GI_ERR_ARG, "attention: a chunk or a cap cannot be negative");
   if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0)
     return gi::fail(GI_ERR_ARG, "attention: %d heads do not divide into %d kv heads", n_heads, n_kv);
   if (hd <= 0 || hd > 256) return gi::fail(GI_ERR_UNSUPPORTED, "attention: head size %d is outside 1..256", hd);
   if (n_seqs > 65535 || n_heads > 65535) return gi::fail(GI_ERR_UNSUPPORTED, "attention: more than 65535 sequences or heads in one launch");
-  const int dpt = max(4, pow2_at_least((hd + 3) / 4));
+  const int dpt = max(4, pow2_at_least((hdv + 3) / 4));
   dim3 grid((max_q_len + QT - 1) / QT, n_heads, n_seqs);
-  const size_t smem = ((size_t)(QT + 2 * KT) * (hd + 1) + (size_t)QT * (KT + 1)) * sizeof(float);
+  const size_t smem = ((size_t)(QT + KT) * (hd + 1) + (size_t)KT * (hdv + 1) + (size_t)QT * (KT + 1)) * sizeof(float);
   GI_DISPATCH_DTYPE(dtype, T,
       return (launch_prefill<T>(dpt, grid, smem, (cudaStream_t)stream, (T*)out, ldo, (const T*)q, ldq, (const T*)kcache,
                                 (const T*)vcache, block_table, max_pages, cu_seqlens, seq_slots, seq_pos0, n_heads, n_kv,
-                                hd, scale, window)));
+                                hd, scale, window, hdv, softcap, sinks, chunk)));
   return GI_OK;
 }
 
@@ -432,7 +485,20 @@ extern "C" int gi_attn_decode_generic(void* out, long ldo, float* part_o, float*
                                       int max_pages, const int* seq_slots, const int* seq_lens, int n_seqs,
                                       int n_heads, int n_kv, int hd, float scale, int window, int n_splits,
                                       int own_tiles, void* stream) {
+  return gi_attn_decode_generic_ex(out, ldo, part_o, part_ml, q, ldq, dtype, kcache, vcache, block_table, max_pages, seq_slots,
+                                   seq_lens, n_seqs, n_heads, n_kv, hd, scale, window, n_splits, own_tiles, hd, 0.f, nullptr, 0,
+                                   stream);
+}
+
+extern "C" int gi_attn_decode_generic_ex(void* out, long ldo, float* part_o, float* part_ml, const void* q, long ldq,
+                                         int dtype, const void* kcache, const void* vcache, const int* block_table,
+                                         int max_pages, const int* seq_slots, const int* seq_lens, int n_seqs,
+                                         int n_heads, int n_kv, int hd, float scale, int window, int n_splits,
+                                         int own_tiles, int hdv, float softcap, const float* sinks, int chunk,
+                                         void* stream) {
   if (n_seqs <= 0) return GI_OK;
+  if (hdv <= 0 || hdv > 256) return gi::fail(GI_ERR_UNSUPPORTED, "attention: value size %d is outside 1..256", hdv);
+  if (chunk < 0 || softcap < 0.f) return gi::fail(GI_ERR_ARG, "attention: a chunk or a cap cannot be negative");
   if (own_tiles < 0) return gi::fail(GI_ERR_ARG, "attention: tiles per slice cannot be negative");
   if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0)
     return gi::fail(GI_ERR_ARG, "attention: %d heads do not divide into %d kv heads", n_heads, n_kv);
@@ -442,10 +508,10 @@ extern "C" int gi_attn_decode_generic(void* out, long ldo, float* part_o, float*
   const int group = n_heads / n_kv;
   const int gc = min(8, pow2_at_least(group));
   const int chunks = (group + gc - 1) / gc;
-  const int dc = pow2_at_least((hd + 31) / 32);
+  const int dc = pow2_at_least((hdv + 31) / 32);
   if ((long)n_kv * chunks > 65535 || n_seqs > 65535) return gi::fail(GI_ERR_UNSUPPORTED, "attention: more than 65535 sequences or kv heads in one launch");
   dim3 grid(n_splits, n_kv * chunks, n_seqs);
-  const size_t smem = ((size_t)gc * hd + 4 * (size_t)gc * hd + 8 * (size_t)gc) * sizeof(float);
+  const size_t smem = ((size_t)gc * hd + 4 * (size_t)gc * hdv + 8 * (size_t)gc) * sizeof(float);
   cudaStream_t s = (cudaStream_t)stream;
   int rc = GI_OK;
 #define GI_GC_CASE(G)                                                                                              \
@@ -453,7 +519,7 @@ extern "C" int gi_attn_decode_generic(void* out, long ldo, float* part_o, float*
     GI_DISPATCH_DTYPE(dtype, T,                                                                                    \
         rc = (launch_decode_dc<T, G>(dc, grid, smem, s, (T*)out, ldo, part_o, part_ml, (const T*)q, ldq, (const T*)kcache, \
                                      (const T*)vcache, block_table, max_pages, seq_slots, seq_lens, n_heads, n_kv, hd, \
-                                     scale, window, n_splits, own_tiles)));                                        \
+                                     scale, window, n_splits, own_tiles, hdv, softcap, sinks, chunk)));            \
     break;
   switch (gc) {
     GI_GC_CASE(1)
@@ -466,7 +532,7 @@ extern "C" int gi_attn_decode_generic(void* out, long ldo, float* part_o, float*
   if (n_splits > 1) {
     dim3 cgrid(n_heads, n_seqs);
     GI_DISPATCH_DTYPE(dtype, T,
-        (attn_combine_kernel<T><<<cgrid, 64, 0, s>>>((T*)out, ldo, part_o, part_ml, n_heads, hd, n_splits)));
+        (attn_combine_kernel<T><<<cgrid, 64, 0, s>>>((T*)out, ldo, part_o, part_ml, n_heads, hdv, n_splits)));
     return gi::check_launch("attention combine");
   }
   return GI_OK;

@@ -8,14 +8,14 @@ namespace {
 // x[t, :] = table[tokens[t], :] as float (the reference's embed: src/cuda.rs:418-432, no scaling).
 template <typename TW>
 __global__ void embed_kernel(float* __restrict__ out, const TW* __restrict__ table, const int* __restrict__ tokens,
-                             int d, int vocab) {
+                             int d, int vocab, float scale) {
   gi::pdl_prologue();
   const int t = blockIdx.x;
   int id = tokens[t];
   if (id < 0 || id >= vocab) id = 0;  // the host validates ids; padding rows may carry anything
   const TW* row = table + (size_t)id * d;
   float* o = out + (size_t)t * d;
-  for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = gi::ldf(row + i);
+  for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = gi::ldf(row + i) * scale;   // scale 1: the value itself
 }
 
 // Sum of the partial sums a deferred product left for features f..f+3 of token m (see gemm_stream.cu: a tile of
@@ -136,15 +136,34 @@ __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, i
   gi::stf(out + i, g / (1.0f + expf(-g)) * u);
 }
 
+// The same with the activation named: 0 silu, 1 gelu in its tanh form, 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))).
+template <typename T>
+__global__ void act_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, int f, size_t total, int interleaved, int act) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const size_t m = i / f, c = i % f;
+  const size_t gate_at = interleaved ? (c / 8) * 16 + c % 8 : c;
+  const size_t up_at = interleaved ? gate_at + 8 : (size_t)f + c;
+  const float g = gi::ldf(gu + m * 2 * (size_t)f + gate_at);
+  const float u = gi::ldf(gu + m * 2 * (size_t)f + up_at);
+  const float a = act == 1 ? 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) : g / (1.0f + expf(-g));
+  gi::stf(out + i, a * u);
+}
+
 }  // namespace
 
 extern "C" int gi_embed(float* out, const void* table, int table_dtype, const int* tokens, int n_tokens, int d,
                         int vocab, void* stream) {
+  return gi_embed_scaled(out, table, table_dtype, tokens, n_tokens, d, vocab, 1.0f, stream);
+}
+
+extern "C" int gi_embed_scaled(float* out, const void* table, int table_dtype, const int* tokens, int n_tokens, int d,
+                               int vocab, float scale, void* stream) {
   if (n_tokens <= 0) return GI_OK;
   if (d <= 0 || vocab <= 0) return gi::fail(GI_ERR_ARG, "embed: bad sizes d=%d vocab=%d", d, vocab);
   cudaError_t e = cudaSuccess;
   GI_DISPATCH_DTYPE(table_dtype, TW,
-                    e = gi::launch(embed_kernel<TW>, dim3(n_tokens), dim3(256), 0, (cudaStream_t)stream, out, (const TW*)table, tokens, d, vocab));
+                    e = gi::launch(embed_kernel<TW>, dim3(n_tokens), dim3(256), 0, (cudaStream_t)stream, out, (const TW*)table, tokens, d, vocab, scale));
   return gi::check(e, "embed");
 }
 
@@ -214,4 +233,15 @@ extern "C" int gi_silu_mul(void* out, const void* gate_up, int dtype, int n_rows
   const unsigned blocks = (unsigned)((total + 255) / 256);
   GI_DISPATCH_DTYPE(dtype, T, silu_mul_kernel<T><<<blocks, 256, 0, (cudaStream_t)stream>>>((T*)out, (const T*)gate_up, f, total, interleaved));
   return gi::check_launch("silu_mul");
+}
+
+extern "C" int gi_act_mul(void* out, const void* gate_up, int dtype, int n_rows, int f, int interleaved, int act, void* stream) {
+  if (n_rows <= 0) return GI_OK;
+  if (f <= 0) return gi::fail(GI_ERR_ARG, "act_mul: bad width %d", f);
+  if (act != 0 && act != 1) return gi::fail(GI_ERR_ARG, "act_mul: unknown activation %d", act);
+  if (interleaved && f % 8 != 0) return gi::fail(GI_ERR_ARG, "act_mul: interleaved rows need a width that is a multiple of 8, got %d", f);
+  const size_t total = (size_t)n_rows * f;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  GI_DISPATCH_DTYPE(dtype, T, act_mul_kernel<T><<<blocks, 256, 0, (cudaStream_t)stream>>>((T*)out, (const T*)gate_up, f, total, interleaved, act));
+  return gi::check_launch("act_mul");
 }

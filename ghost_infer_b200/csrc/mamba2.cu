@@ -1,0 +1,275 @@
+// The Mamba-2 (state-space duality) mixer's own steps, between its input and output projections.
+//
+// The input projection's rows are [z: inner | x: inner | B: G*N | C: G*N | dt: heads], inner = heads * P.
+//  * conv:  the channels [x | B | C] pass a causal convolution over `taps` tokens per channel, plus bias, then silu.
+//           Inputs before a step's first token come from the sequence's state (zeros for a fresh sequence).
+//  * scan:  dt <- softplus(dt + dt_bias); per head (head h reads group h / (heads / G) of B and C)
+//           S <- exp(-exp(A_log) dt) S + dt B x^T   (S is N x P),   y = S^T C + D x.
+//           Everything here is 32-bit; the tokens of a sequence are walked in order, sixteen at a time through shared
+//           memory; a thread owns one column p of S and a run of its rows n, kept in registers across the step.
+//           One token or a thousand take the same arithmetic in the same order, so cutting a prompt changes no bit.
+//  * gate + norm: y * silu(z), divided by the root mean square of each of `parts` equal parts, times a weight.
+// Per-sequence state: one float row per slot, [S: heads * N * P | last taps - 1 conv inputs: (taps - 1) * channels];
+// slot -1 (a padding row of a fixed-size launch) uses the last row of the matrix.
+#include <math.h>
+
+#include "api.h"
+#include "common.cuh"
+
+namespace {
+
+constexpr int CH = 16;   // tokens per trip through shared memory in the scan
+
+__device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
+__device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log1pf(expf(v)); }
+
+// grid (token tiles of 8, sequences); threads walk channels
+template <typename T, typename TW>
+__global__ void __launch_bounds__(256)
+conv_kernel(T* __restrict__ out, const T* __restrict__ proj, long ld_proj, const TW* __restrict__ w,
+            const TW* __restrict__ bias, const float* __restrict__ state, long state_ld, int state_rows,
+            const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slots, int inner, int channels, int taps,
+            int s_floats) {
+  gi::pdl_prologue();
+  const int b = blockIdx.y;
+  const int tok0 = cu_seqlens[b], qlen = cu_seqlens[b + 1] - tok0;
+  const int i0 = blockIdx.x * 8;
+  if (i0 >= qlen) return;
+  const int slot = seq_slots[b];
+  const float* cs = state + (size_t)(slot >= 0 ? slot : state_rows - 1) * state_ld + s_floats;
+  const int n_here = min(8, qlen - i0);
+  for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+    const float bc = gi::ldf(bias + c);
+    for (int ii = 0; ii < n_here; ++ii) {
+      const int i = i0 + ii;
+      float acc = bc;
+      for (int j = 0; j < taps; ++j) {
+        const int src = i - (taps - 1) + j;
+        const float v = src >= 0 ? gi::ldf(proj + (size_t)(tok0 + src) * ld_proj + inner + c)
+                                 : cs[(size_t)(src + taps - 1) * channels + c];
+        acc = fmaf(gi::ldf(w + (size_t)c * taps + j), v, acc);
+      }
+      gi::stf(out + (size_t)(tok0 + i) * channels + c, silu_f(acc));
+    }
+  }
+}
+
+// grid (channel blocks, sequences): the state takes the last taps - 1 inputs of [old state | this step's inputs]
+template <typename T>
+__global__ void conv_update_kernel(const T* __restrict__ proj, long ld_proj, float* __restrict__ state, long state_ld,
+                                   int state_rows, const int* __restrict__ cu_seqlens,
+                                   const int* __restrict__ seq_slots, int inner, int channels, int taps, int s_floats) {
+  gi::pdl_prologue();
+  const int b = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= channels) return;
+  const int tok0 = cu_seqlens[b], qlen = cu_seqlens[b + 1] - tok0;
+  if (qlen <= 0) return;
+  const int slot = seq_slots[b];
+  float* cs = state + (size_t)(slot >= 0 ? slot : state_rows - 1) * state_ld + s_floats;
+  const int keep = taps - 1;
+  // place k of the new state is place qlen + k of [old state (keep) | inputs (qlen)]; walking k upwards reads old
+  // places qlen + k > k only, which are not yet overwritten
+  for (int k = 0; k < keep; ++k) {
+    const int at = qlen + k;
+    const float v = at < keep ? cs[(size_t)at * channels + c] : gi::ldf(proj + (size_t)(tok0 + at - keep) * ld_proj + inner + c);
+    cs[(size_t)k * channels + c] = v;
+  }
+}
+
+// grid (heads, sequences, column tiles of PT); block PT * NS threads: thread (pl, ns) owns rows ns*NPT.. of column p0+pl
+template <typename T, typename TW, int NPT>
+__global__ void scan_kernel(float* __restrict__ y, const T* __restrict__ xbc, const T* __restrict__ proj, long ld_proj,
+                            const TW* __restrict__ dt_bias, const TW* __restrict__ a_log, const TW* __restrict__ d_skip,
+                            float* __restrict__ state, long state_ld, int state_rows,
+                            const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slots, int heads, int P, int N,
+                            int groups, int PT, int NS) {
+  extern __shared__ float sm[];
+  float* sx = sm;                    // [CH][PT]
+  float* sB = sx + CH * PT;          // [CH][N]
+  float* sC = sB + CH * N;           // [CH][N]
+  float* sdt = sC + CH * N;          // [CH]
+  float* sdA = sdt + CH;             // [CH]
+  float* part = sdA + CH;            // [CH][NS][PT]
+  gi::pdl_prologue();
+  const int h = blockIdx.x, b = blockIdx.y, p0 = blockIdx.z * PT;
+  const int tok0 = cu_seqlens[b], qlen = cu_seqlens[b + 1] - tok0;
+  if (qlen <= 0) return;
+  const int slot = seq_slots[b];
+  float* S_row = state + (size_t)(slot >= 0 ? slot : state_rows - 1) * state_ld + (size_t)h * N * P;
+  const int g = h / (heads / groups);
+  const int inner = heads * P, channels = inner + 2 * groups * N;
+  const int tid = threadIdx.x, nthreads = blockDim.x;
+  const int pl = tid % PT, ns = tid / PT, p = p0 + pl, n_lo = ns * NPT;
+  const bool p_ok = p < P;
+  float S[NPT];
+#pragma unroll
+  for (int i = 0; i < NPT; ++i) S[i] = (p_ok && n_lo + i < N) ? S_row[(size_t)(n_lo + i) * P + p] : 0.f;
+  const float A = -expf(gi::ldf(a_log + h)), D = gi::ldf(d_skip + h), bias = gi::ldf(dt_bias + h);
+
+  for (int c0 = 0; c0 < qlen; c0 += CH) {
+    const int nc = min(CH, qlen - c0);
+    __syncthreads();
+    for (int idx = tid; idx < nc * PT; idx += nthreads) {
+      const int t = idx / PT, j = idx % PT;
+      sx[idx] = (p0 + j < P) ? gi::ldf(xbc + (size_t)(tok0 + c0 + t) * channels + (size_t)h * P + p0 + j) : 0.f;
+    }
+    for (int idx = tid; idx < nc * N; idx += nthreads) {
+      const int t = idx / N, n = idx % N;
+      const T* r = xbc + (size_t)(tok0 + c0 + t) * channels + inner + (size_t)g * N + n;
+      sB[idx] = gi::ldf(r);
+      sC[idx] = gi::ldf(r + (size_t)groups * N);
+    }
+    for (int t = tid; t < nc; t += nthreads) {
+      const float dt = softplus_f(gi::ldf(proj + (size_t)(tok0 + c0 + t) * ld_proj + 2 * inner + 2 * groups * N + h) + bias);
+      sdt[t] = dt;
+      sdA[t] = expf(A * dt);
+    }
+    __syncthreads();
+    for (int t = 0; t < nc; ++t) {
+      const float dA = sdA[t], dtx = sdt[t] * sx[t * PT + pl];
+      const float* Bt = sB + t * N + n_lo;
+      const float* Ct = sC + t * N + n_lo;
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < NPT; ++i) {
+        if (n_lo + i < N) {
+          S[i] = fmaf(dA, S[i], dtx * Bt[i]);
+          acc = fmaf(S[i], Ct[i], acc);
+        }
+      }
+      part[(t * NS + ns) * PT + pl] = acc;
+    }
+    __syncthreads();
+    for (int idx = tid; idx < nc * PT; idx += nthreads) {
+      const int t = idx / PT, j = idx % PT;
+      if (p0 + j >= P) continue;
+      float sum = 0.f;
+      for (int s = 0; s < NS; ++s) sum += part[(t * NS + s) * PT + j];
+      y[(size_t)(tok0 + c0 + t) * inner + (size_t)h * P + p0 + j] = sum + D * sx[idx];
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < NPT; ++i)
+    if (p_ok && n_lo + i < N) S_row[(size_t)(n_lo + i) * P + p] = S[i];
+}
+
+// grid (tokens, parts)
+template <typename TO, typename T, typename TW>
+__global__ void __launch_bounds__(256)
+gate_norm_kernel(TO* __restrict__ out, const float* __restrict__ y, const T* __restrict__ proj, long ld_proj,
+                 const TW* __restrict__ w, int inner, int parts, float eps) {
+  __shared__ float scratch[33];
+  gi::pdl_prologue();
+  const int t = blockIdx.x, part = blockIdx.y, gw = inner / parts, c0 = part * gw;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < gw; i += blockDim.x) {
+    const float v = y[(size_t)t * inner + c0 + i] * silu_f(gi::ldf(proj + (size_t)t * ld_proj + c0 + i));
+    ss = fmaf(v, v, ss);
+  }
+  ss = gi::block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)gw + eps);
+  for (int i = threadIdx.x; i < gw; i += blockDim.x) {
+    const float v = y[(size_t)t * inner + c0 + i] * silu_f(gi::ldf(proj + (size_t)t * ld_proj + c0 + i));
+    gi::stf(out + (size_t)t * inner + c0 + i, v * inv * gi::ldf(w + c0 + i));
+  }
+}
+
+template <typename T, typename TW, int NPT>
+int launch_scan(dim3 grid, int threads, size_t smem, cudaStream_t s, float* y, const T* xbc, const T* proj, long ld_proj,
+                const TW* dt_bias, const TW* a_log, const TW* d_skip, float* state, long state_ld, int state_rows,
+                const int* cu, const int* slots, int heads, int P, int N, int groups, int PT, int NS) {
+  auto kern = scan_kernel<T, TW, NPT>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return gi::fail(GI_ERR_CUDA, "mamba2 scan: %s", cudaGetErrorString(e));
+  }
+  return gi::check(gi::launch(kern, grid, dim3(threads), smem, s, y, xbc, proj, ld_proj, dt_bias, a_log, d_skip, state,
+                              state_ld, state_rows, cu, slots, heads, P, N, groups, PT, NS), "mamba2 scan");
+}
+
+}  // namespace
+
+extern "C" int gi_mamba2_conv(void* xbc_out, const void* proj, int dtype, long ld_proj, const void* conv_w,
+                              const void* conv_b, int w_dtype, const float* state, long state_ld, int state_rows,
+                              const int* cu_seqlens, const int* seq_slots, int n_seqs, int max_q_len, int inner,
+                              int channels, int taps, int s_floats, void* stream) {
+  if (n_seqs <= 0 || max_q_len <= 0) return GI_OK;
+  if (taps < 1 || channels <= 0 || inner <= 0) return gi::fail(GI_ERR_ARG, "mamba2 conv: bad sizes");
+  if (n_seqs > 65535) return gi::fail(GI_ERR_UNSUPPORTED, "mamba2 conv: more than 65535 sequences in one launch");
+  dim3 grid((max_q_len + 7) / 8, n_seqs);
+  cudaError_t e = cudaSuccess;
+  GI_DISPATCH_DTYPE(dtype, T, GI_DISPATCH_DTYPE(w_dtype, TW,
+      e = gi::launch(conv_kernel<T, TW>, grid, dim3(256), 0, (cudaStream_t)stream, (T*)xbc_out, (const T*)proj, ld_proj,
+                     (const TW*)conv_w, (const TW*)conv_b, state, state_ld, state_rows, cu_seqlens, seq_slots, inner, channels,
+                     taps, s_floats)));
+  return gi::check(e, "mamba2 conv");
+}
+
+extern "C" int gi_mamba2_conv_update(const void* proj, int dtype, long ld_proj, float* state, long state_ld, int state_rows,
+                                     const int* cu_seqlens, const int* seq_slots, int n_seqs, int inner, int channels,
+                                     int taps, int s_floats, void* stream) {
+  if (n_seqs <= 0 || taps <= 1) return GI_OK;
+  if (n_seqs > 65535) return gi::fail(GI_ERR_UNSUPPORTED, "mamba2 conv: more than 65535 sequences in one launch");
+  dim3 grid((channels + 127) / 128, n_seqs);
+  cudaError_t e = cudaSuccess;
+  GI_DISPATCH_DTYPE(dtype, T,
+      e = gi::launch(conv_update_kernel<T>, grid, dim3(128), 0, (cudaStream_t)stream, (const T*)proj, ld_proj, state, state_ld,
+                     state_rows, cu_seqlens, seq_slots, inner, channels, taps, s_floats));
+  return gi::check(e, "mamba2 conv update");
+}
+
+extern "C" int gi_mamba2_scan(float* y, const void* xbc, const void* proj, int dtype, long ld_proj, const void* dt_bias,
+                              const void* a_log, const void* d_skip, int w_dtype, float* state, long state_ld,
+                              int state_rows, const int* cu_seqlens, const int* seq_slots, int n_seqs, int heads, int P,
+                              int N, int groups, void* stream) {
+  if (n_seqs <= 0) return GI_OK;
+  if (heads <= 0 || P <= 0 || N <= 0 || groups <= 0 || heads % groups != 0)
+    return gi::fail(GI_ERR_ARG, "mamba2 scan: %d heads, %d groups, head size %d, state %d", heads, groups, P, N);
+  if (n_seqs > 65535 || heads > 65535) return gi::fail(GI_ERR_UNSUPPORTED, "mamba2 scan: more than 65535 sequences or heads");
+  // a block takes up to 64 columns of one head's state; a thread the fewest rows (a power of two, at most 64) for
+  // which the block stays within 256 threads where that is possible
+  const int PT = P < 64 ? P : 64;
+  int npt = 1;
+  while (npt < 64 && PT * ((N + npt - 1) / npt) > 256) npt *= 2;
+  const int NS = (N + npt - 1) / npt;
+  const int threads = PT * NS;
+  if (threads > 1024) return gi::fail(GI_ERR_UNSUPPORTED, "mamba2 scan: a state of %d rows is more than one block takes", N);
+  dim3 grid(heads, n_seqs, (P + PT - 1) / PT);
+  const size_t smem = ((size_t)CH * PT + 2 * (size_t)CH * N + 2 * CH + (size_t)CH * NS * PT) * sizeof(float);
+  cudaStream_t s = (cudaStream_t)stream;
+  int rc = GI_OK;
+#define GI_SCAN_CASE(NPT)                                                                                              \
+  case NPT:                                                                                                            \
+    GI_DISPATCH_DTYPE(dtype, T, GI_DISPATCH_DTYPE(w_dtype, TW,                                                         \
+        rc = (launch_scan<T, TW, NPT>(grid, threads, smem, s, y, (const T*)xbc, (const T*)proj, ld_proj, (const TW*)dt_bias, \
+                                      (const TW*)a_log, (const TW*)d_skip, state, state_ld, state_rows, cu_seqlens,    \
+                                      seq_slots, heads, P, N, groups, PT, NS))));                                      \
+    break;
+  switch (npt) {
+    GI_SCAN_CASE(1)
+    GI_SCAN_CASE(2)
+    GI_SCAN_CASE(4)
+    GI_SCAN_CASE(8)
+    GI_SCAN_CASE(16)
+    GI_SCAN_CASE(32)
+    GI_SCAN_CASE(64)
+  }
+#undef GI_SCAN_CASE
+  return rc;
+}
+
+extern "C" int gi_mamba2_gate_norm(void* out, int out_dtype, const float* y, const void* proj, int dtype, long ld_proj,
+                                   const void* w, int w_dtype, int n_tokens, int inner, int parts, float eps,
+                                   void* stream) {
+  if (n_tokens <= 0) return GI_OK;
+  if (parts <= 0 || inner <= 0 || inner % parts != 0)
+    return gi::fail(GI_ERR_ARG, "mamba2 norm: %d values do not divide into %d parts", inner, parts);
+  if (parts > 65535) return gi::fail(GI_ERR_UNSUPPORTED, "mamba2 norm: more than 65535 parts");
+  dim3 grid(n_tokens, parts);
+  cudaError_t e = cudaSuccess;
+  GI_DISPATCH_DTYPE(out_dtype, TO, GI_DISPATCH_DTYPE(dtype, T, GI_DISPATCH_DTYPE(w_dtype, TW,
+      e = gi::launch(gate_norm_kernel<TO, T, TW>, grid, dim3(256), 0, (cudaStream_t)stream, (TO*)out, y, (const T*)proj, ld_proj,
+                     (const TW*)w, inner, parts, eps))));
+  return gi::check(e, "mamba2 norm");
+}

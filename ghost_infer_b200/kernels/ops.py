@@ -68,6 +68,20 @@ def _bind():
         "gi_attn_decode_kr": [P, L, P, P, P, L, P, P, P, I, P, P, I, I, I, I, F, I, I, I, I, I, P],
         "gi_gemm_tc_qkv_rope": [P, P, P, I, I, I, L, L, L, P, P, P, P, I, P, P, I, I, I, I, P],
         "gi_sample": [P, P, L, I, I, F, I, F, P, P, P],
+        "gi_embed_scaled": [P, P, I, P, I, I, I, F, P],
+        "gi_act_mul": [P, P, I, I, I, I, I, P],
+        "gi_attn_prefill_generic_ex": [P, L, P, L, I, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, F, P, I, P],
+        "gi_attn_decode_generic_ex": [P, L, P, P, P, L, I, P, P, P, I, P, P, I, I, I, I, F, I, I, I, I, F, P, I, P],
+        "gi_kv_store": [P, I, L, P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, P],
+        "gi_mamba2_conv": [P, P, I, L, P, P, I, P, L, I, P, P, I, I, I, I, I, I, P],
+        "gi_mamba2_conv_update": [P, I, L, P, L, I, P, P, I, I, I, I, I, P],
+        "gi_mamba2_scan": [P, P, P, I, L, P, P, P, I, P, L, I, P, P, I, I, I, I, I, P],
+        "gi_mamba2_gate_norm": [P, I, P, P, I, L, P, I, I, I, I, F, P],
+        "gi_moe_route": [P, P, P, P, I, L, P, P, I, I, I, I, I, P],
+        "gi_moe_plan": [P, P, P, P, P, I, I, P],
+        "gi_moe_gemm_gate_up": [P, I, P, L, P, I, L, P, P, I, I, I, I, I, P],
+        "gi_moe_gemm_down": [P, P, I, L, P, I, L, P, I, I, I, I, P],
+        "gi_moe_combine": [P, P, P, P, P, P, I, I, I, P],
     }
     for name, argtypes in sigs.items():
         fn = getattr(lib, name)
@@ -203,7 +217,8 @@ def profile_stop() -> Dict[str, float]:
 
 
 # ------------------------------------------------------------------------------------------------
-def embed(table: torch.Tensor, tokens: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+def embed(table: torch.Tensor, tokens: torch.Tensor, out: Optional[torch.Tensor] = None, scale: float = 1.0) -> torch.Tensor:
+    """x[t] = table[tokens[t]] * scale as float32 rows."""
     lib = _bind()
     _cuda(table, "embedding table")
     if table.dim() != 2 or not table.is_contiguous():
@@ -211,8 +226,8 @@ def embed(table: torch.Tensor, tokens: torch.Tensor, out: Optional[torch.Tensor]
     n, (vocab, d) = tokens.numel(), table.shape
     if out is None:
         out = torch.empty((n, d), dtype=torch.float32, device=table.device)
-    _check(lib, lib.gi_embed(out.data_ptr(), table.data_ptr(), _dt(table, "embedding table"), _i32(tokens, "tokens"),
-                             n, d, vocab, _stream()))
+    _check(lib, lib.gi_embed_scaled(out.data_ptr(), table.data_ptr(), _dt(table, "embedding table"), _i32(tokens, "tokens"),
+                                    n, d, vocab, float(scale), _stream()))
     return out
 
 
@@ -793,17 +808,22 @@ def rope_cache_write(qkv: torch.Tensor, table: Optional[torch.Tensor], positions
 def attn_prefill_generic(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_table: torch.Tensor,
                          cu_seqlens: torch.Tensor, seq_slots: torch.Tensor, seq_pos0: torch.Tensor, n_seqs: int,
                          max_q_len: int, n_heads: int, n_kv: int, head_dim: int, scale: float,
-                         window: Optional[int], out: torch.Tensor) -> torch.Tensor:
+                         window: Optional[int], out: torch.Tensor, *, v_dim: Optional[int] = None, softcap: float = 0.0,
+                         sinks: Optional[torch.Tensor] = None, chunk: Optional[int] = None) -> torch.Tensor:
+    """`v_dim`: width of a value head when it is not the keys' (`vcache` is then [pages, kv heads, 64, v_dim]);
+    `softcap` > 0: scores become cap * tanh(score / cap); `sinks` float32 [heads]: a term exp(sink) in each head's
+    softmax denominator without key or value; `chunk`: a query sees keys of its own chunk floor(pos / chunk) only."""
     lib = _bind()
     _cuda(q, "queries")
     ldq, ldo = _rows(q, "queries"), _rows(out, "attention output")
     if kcache.dtype != q.dtype or out.dtype != q.dtype:
         raise KernelError("queries, cache and attention output must share a dtype")
-    _check(lib, lib.gi_attn_prefill_generic(
+    _check(lib, lib.gi_attn_prefill_generic_ex(
         out.data_ptr(), ldo, q.data_ptr(), ldq, _dt(q, "queries"), kcache.data_ptr(), vcache.data_ptr(),
         _i32(block_table, "block table"), block_table.shape[1], _i32(cu_seqlens, "cu_seqlens"),
         _i32(seq_slots, "slots"), _i32(seq_pos0, "start positions"), n_seqs, max_q_len, n_heads, n_kv, head_dim,
-        float(scale), int(window or 0), _stream()))
+        float(scale), int(window or 0), int(v_dim or head_dim), float(softcap or 0.0), _sinks_ptr(sinks, n_heads),
+        int(chunk or 0), _stream()))
     return out
 
 
@@ -811,8 +831,10 @@ def attn_decode_generic(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Ten
                         seq_slots: torch.Tensor, seq_lens: torch.Tensor, n_seqs: int, n_heads: int, n_kv: int,
                         head_dim: int, scale: float, window: Optional[int], n_splits: int, out: torch.Tensor,
                         part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None,
-                        own_tiles: int = 0) -> torch.Tensor:
-    """`own_tiles` > 0: slice s of a sequence is tiles [s * own_tiles, (s + 1) * own_tiles) of its own span (32 keys a
+                        own_tiles: int = 0, *, v_dim: Optional[int] = None, softcap: float = 0.0,
+                        sinks: Optional[torch.Tensor] = None, chunk: Optional[int] = None) -> torch.Tensor:
+    """`v_dim`, `softcap`, `sinks`, `chunk`: as `attn_prefill_generic`'s.
+    `own_tiles` > 0: slice s of a sequence is tiles [s * own_tiles, (s + 1) * own_tiles) of its own span (32 keys a
     tile), whatever `n_splits` is, which must then cover the longest sequence; 0: every span is cut into `n_splits`
     equal slices."""
     lib = _bind()
@@ -823,17 +845,27 @@ def attn_decode_generic(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Ten
     if n_splits > 1:
         if part_o is None or part_ml is None:
             raise KernelError("attention slices need scratch memory")
-        if part_o.dtype != torch.float32 or part_o.numel() < n_seqs * n_heads * n_splits * head_dim:
+        if part_o.dtype != torch.float32 or part_o.numel() < n_seqs * n_heads * n_splits * int(v_dim or head_dim):
             raise KernelError("attention scratch for outputs is too small")
         if part_ml.dtype != torch.float32 or part_ml.numel() < n_seqs * n_heads * n_splits * 2:
             raise KernelError("attention scratch for maxima and sums is too small")
-    _check(lib, lib.gi_attn_decode_generic(
+    _check(lib, lib.gi_attn_decode_generic_ex(
         out.data_ptr(), ldo, part_o.data_ptr() if part_o is not None else None,
         part_ml.data_ptr() if part_ml is not None else None, q.data_ptr(), ldq, _dt(q, "queries"),
         kcache.data_ptr(), vcache.data_ptr(), _i32(block_table, "block table"), block_table.shape[1],
         _i32(seq_slots, "slots"), _i32(seq_lens, "lengths"), n_seqs, n_heads, n_kv, head_dim, float(scale),
-        int(window or 0), int(n_splits), int(own_tiles), _stream()), 2 if n_splits > 1 else 1)
+        int(window or 0), int(n_splits), int(own_tiles), int(v_dim or head_dim), float(softcap or 0.0),
+        _sinks_ptr(sinks, n_heads), int(chunk or 0), _stream()), 2 if n_splits > 1 else 1)
     return out
+
+
+def _sinks_ptr(sinks: Optional[torch.Tensor], n_heads: int):
+    if sinks is None:
+        return None
+    if sinks.dtype != torch.float32 or not sinks.is_contiguous() or sinks.numel() != n_heads:
+        raise KernelError(f"attention sinks must be {n_heads} contiguous float32 values, one per head")
+    _cuda(sinks, "attention sinks")
+    return sinks.data_ptr()
 
 
 def attn_prefill_tc(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_table: torch.Tensor,
@@ -1171,3 +1203,246 @@ def attention(qkv: torch.Tensor, memory, step, n_heads: int, n_kv: int, head_dim
         kernel = attn_prefill_generic
     return kernel(qkv, memory.k, memory.v, memory.block_table, step.cu_seqlens, step.seq_slots,
                   step.seq_pos0, step.n_seqs, step.max_q_len, n_heads, n_kv, head_dim, scale, window, out)
+
+
+# ------------------------------------------------------------------------------------------------
+# Attention without rotation whose values may be blended with another layer's and have a width of their own.
+def kv_store(qkv: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, memory, n_heads: int, n_kv: int,
+             head_dim: int, v_dim: int, first: Optional[torch.Tensor] = None, blend: Optional[torch.Tensor] = None,
+             copy_to: Optional[torch.Tensor] = None) -> None:
+    """Keys and values of packed rows [q | k | v] into `memory`'s pages, unrotated.  `first` [tokens, kv heads * v_dim]
+    and `blend` (one float32 on the device): the values become (1 - blend) v + blend first beforehand (also in the rows);
+    `copy_to`: receives the rows' own values."""
+    lib = _bind()
+    _cuda(qkv, "q/k/v rows")
+    ld = _rows(qkv, "q/k/v rows")
+    n = qkv.shape[0]
+    vw = n_kv * v_dim
+    if qkv.shape[1] != (n_heads + n_kv) * head_dim + vw:
+        raise KernelError(f"q/k/v rows are {qkv.shape[1]} wide, wanted {(n_heads + n_kv) * head_dim + vw}")
+    for t, what in ((first, "the first layer's values"), (copy_to, "the copy of the values")):
+        if t is not None and (t.dtype != qkv.dtype or tuple(t.shape) != (n, vw) or not t.is_contiguous()):
+            raise KernelError(f"{what} must be contiguous [{n}, {vw}] {qkv.dtype}")
+    if first is not None and (blend is None or blend.dtype != torch.float32 or blend.numel() != 1 or not blend.is_cuda):
+        raise KernelError("blending values needs its weight as one float32 on the device")
+    write = bool(memory.writes and memory.k is not None)
+    if write:
+        if memory.k.dtype != qkv.dtype or memory.v.dtype != qkv.dtype:
+            raise KernelError(f"the cache is {memory.k.dtype}, the step runs in {qkv.dtype}")
+        if (tuple(memory.k.shape[1:]) != (n_kv, 64, head_dim) or tuple(memory.v.shape[1:]) != (n_kv, 64, v_dim)
+                or not memory.k.is_contiguous() or not memory.v.is_contiguous()):
+            raise KernelError(f"cache pages must be contiguous [pages, {n_kv}, 64, {head_dim}] and [.., {v_dim}], got "
+                              f"{tuple(memory.k.shape)} and {tuple(memory.v.shape)}")
+    bt = memory.block_table
+    _check(lib, lib.gi_kv_store(
+        qkv.data_ptr(), _dt(qkv, "q/k/v rows"), ld, first.data_ptr() if first is not None else None,
+        blend.data_ptr() if first is not None else None, copy_to.data_ptr() if copy_to is not None else None,
+        _i32(positions, "positions"), _i32(slots, "slots"), _i32(bt, "block table"), bt.shape[1] if bt is not None else 0,
+        memory.k.data_ptr() if write else None, memory.v.data_ptr() if write else None, n, n_heads, n_kv, head_dim, v_dim,
+        int(write), _stream()))
+
+
+def attention_general(qkv: torch.Tensor, memory, step, n_heads: int, n_kv: int, head_dim: int, v_dim: int, scale: float,
+                      out: torch.Tensor, *, window: Optional[int] = None, chunk: Optional[int] = None, softcap: float = 0.0,
+                      sinks: Optional[torch.Tensor] = None, plan=None) -> torch.Tensor:
+    """Attention of a step's tokens over the cache with any of: values of another width than the keys, capped scores,
+    a sink per head, chunks of positions, a window.  The cache already holds the step's own keys and values."""
+    if memory.k is None:
+        raise KernelError("attention needs a cache to read from")
+    opts = dict(v_dim=v_dim, softcap=softcap, sinks=sinks, chunk=chunk)
+    if step.is_decode:
+        if plan is None:
+            plan = attn_general_decode_plan(step.n_seqs, step.max_kv_len, step.sm_count, n_heads, n_kv, window, chunk, qkv.dtype)
+        n_splits, own_tiles = plan
+        part_o = part_ml = None
+        if n_splits > 1:
+            part_o = torch.empty((step.n_seqs * n_heads * n_splits * v_dim,), dtype=torch.float32, device=qkv.device)
+            part_ml = torch.empty((step.n_seqs * n_heads * n_splits * 2,), dtype=torch.float32, device=qkv.device)
+        return attn_decode_generic(qkv, memory.k, memory.v, memory.block_table, step.seq_slots, step.seq_lens, step.n_seqs,
+                                   n_heads, n_kv, head_dim, scale, window, n_splits, out, part_o, part_ml, own_tiles=own_tiles,
+                                   **opts)
+    return attn_prefill_generic(qkv, memory.k, memory.v, memory.block_table, step.cu_seqlens, step.seq_slots, step.seq_pos0,
+                                step.n_seqs, step.max_q_len, n_heads, n_kv, head_dim, scale, window, out, **opts)
+
+
+def attn_general_decode_plan(n_seqs: int, max_kv_len: int, sm_count: int, n_heads: int, n_kv: int, window: Optional[int],
+                             chunk: Optional[int], dtype: torch.dtype):
+    """(slices in the launch, tiles per slice) for one-token steps of `attention_general`: slices of eight 32-key tiles
+    counted from the start of the span a query can see (the last `window` positions, its chunk, or everything), so
+    that a sequence's sums are formed in the same order whatever else the step holds."""
+    span = max_kv_len
+    for limit in (window, chunk):
+        if limit:
+            span = min(span, int(limit) + 31)
+    tiles = (span + 31) // 32 + (1 if (window or chunk) else 0)
+    return max(1, (tiles + OWN_LENGTH_TILES - 1) // OWN_LENGTH_TILES), OWN_LENGTH_TILES
+
+
+def act_mul(gate_up: torch.Tensor, act: str, out: Optional[torch.Tensor] = None, interleaved: bool = False) -> torch.Tensor:
+    """act(gate) * up over rows [gate | up]; `act` "silu" or "gelu_tanh"."""
+    lib = _bind()
+    _cuda(gate_up, "gate/up rows")
+    if gate_up.dim() != 2 or not gate_up.is_contiguous() or gate_up.shape[1] % 2:
+        raise KernelError("gate/up rows must be a contiguous [rows, 2 * width] matrix")
+    try:
+        code = {"silu": 0, "gelu_tanh": 1}[act]
+    except KeyError:
+        raise KernelError(f"unknown activation \"{act}\" (silu, gelu_tanh)") from None
+    n, f = gate_up.shape[0], gate_up.shape[1] // 2
+    if out is None:
+        out = torch.empty((n, f), dtype=gate_up.dtype, device=gate_up.device)
+    _check(lib, lib.gi_act_mul(out.data_ptr(), gate_up.data_ptr(), _dt(gate_up, "gate/up rows"), n, f, int(interleaved), code,
+                               _stream()))
+    return out
+
+
+# ------------------------------------------------------------------------------------------------
+# Mamba-2: the steps between its two projections.  `state` is the mixer's per-sequence memory, float32
+# [slots + 1, S floats + (taps - 1) * channels].
+def _mamba_state(state: torch.Tensor, s_floats: int, channels: int, taps: int):
+    if state is None or state.dtype != torch.float32 or state.dim() != 2 or not state.is_contiguous():
+        raise KernelError("the state-space mixer needs its per-sequence state as a contiguous float32 matrix")
+    if state.shape[1] != s_floats + (taps - 1) * channels:
+        raise KernelError(f"state rows hold {state.shape[1]} floats, wanted {s_floats + (taps - 1) * channels}")
+    _cuda(state, "state")
+
+
+def mamba2_conv(proj: torch.Tensor, conv_w: torch.Tensor, conv_b: torch.Tensor, state: torch.Tensor, step, inner: int,
+                channels: int, taps: int, s_floats: int) -> torch.Tensor:
+    """silu(conv(x | B | C)) for the step's tokens, [tokens, channels] in the rows' type; then the state takes the step's
+    last inputs."""
+    lib = _bind()
+    _cuda(proj, "projected rows")
+    ld = _rows(proj, "projected rows")
+    _mamba_state(state, s_floats, channels, taps)
+    if tuple(conv_w.shape) != (channels, taps) or not conv_w.is_contiguous() or conv_b.numel() != channels or conv_w.dtype != conv_b.dtype:
+        raise KernelError(f"convolution weights must be [{channels}, {taps}] with {channels} biases of the same type")
+    out = torch.empty((proj.shape[0], channels), dtype=proj.dtype, device=proj.device)
+    _check(lib, lib.gi_mamba2_conv(out.data_ptr(), proj.data_ptr(), _dt(proj, "projected rows"), ld, conv_w.data_ptr(),
+                                   conv_b.data_ptr(), _dt(conv_w, "convolution weights"), state.data_ptr(), state.stride(0),
+                                   state.shape[0], _i32(step.cu_seqlens, "cu_seqlens"), _i32(step.seq_slots, "slots"),
+                                   step.n_seqs, step.max_q_len, inner, channels, taps, s_floats, _stream()))
+    _check(lib, lib.gi_mamba2_conv_update(proj.data_ptr(), _dt(proj, "projected rows"), ld, state.data_ptr(), state.stride(0),
+                                          state.shape[0], _i32(step.cu_seqlens, "cu_seqlens"), _i32(step.seq_slots, "slots"),
+                                          step.n_seqs, inner, channels, taps, s_floats, _stream()), 1 if taps > 1 else 0)
+    return out
+
+
+def mamba2_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor, d_skip: torch.Tensor,
+                state: torch.Tensor, step, heads: int, head_dim: int, n_state: int, groups: int, taps: int) -> torch.Tensor:
+    """The recurrence over the step's tokens from and into `state`; float32 [tokens, heads * head_dim]."""
+    lib = _bind()
+    _cuda(xbc, "convolved rows")
+    _cuda(proj, "projected rows")
+    inner = heads * head_dim
+    channels = inner + 2 * groups * n_state
+    _mamba_state(state, heads * n_state * head_dim, channels, taps)
+    if xbc.dtype != proj.dtype or tuple(xbc.shape) != (proj.shape[0], channels) or not xbc.is_contiguous():
+        raise KernelError(f"convolved rows must be contiguous [{proj.shape[0]}, {channels}] of the projected rows' type")
+    if proj.shape[1] != 2 * inner + 2 * groups * n_state + heads:
+        raise KernelError(f"projected rows are {proj.shape[1]} wide, wanted {2 * inner + 2 * groups * n_state + heads}")
+    for t in (dt_bias, a_log, d_skip):
+        if t.numel() != heads or t.dtype != dt_bias.dtype or not t.is_contiguous():
+            raise KernelError(f"the recurrence's per-head constants must be {heads} values of one type")
+    y = torch.empty((proj.shape[0], inner), dtype=torch.float32, device=proj.device)
+    _check(lib, lib.gi_mamba2_scan(y.data_ptr(), xbc.data_ptr(), proj.data_ptr(), _dt(proj, "projected rows"),
+                                   _rows(proj, "projected rows"), dt_bias.data_ptr(), a_log.data_ptr(), d_skip.data_ptr(),
+                                   _dt(dt_bias, "per-head constants"), state.data_ptr(), state.stride(0), state.shape[0],
+                                   _i32(step.cu_seqlens, "cu_seqlens"), _i32(step.seq_slots, "slots"), step.n_seqs, heads,
+                                   head_dim, n_state, groups, _stream()))
+    return y
+
+
+def mamba2_gate_norm(y: torch.Tensor, proj: torch.Tensor, weight: torch.Tensor, parts: int, eps: float,
+                     out_dtype: torch.dtype) -> torch.Tensor:
+    """rmsnorm in `parts` equal parts of y * silu(z) (z: the first columns of `proj`), times `weight`."""
+    lib = _bind()
+    _cuda(y, "recurrence output")
+    n, inner = y.shape
+    if y.dtype != torch.float32 or not y.is_contiguous() or weight.numel() != inner or not weight.is_contiguous():
+        raise KernelError("the gated norm takes contiguous float32 rows and one weight per value")
+    out = torch.empty((n, inner), dtype=out_dtype, device=y.device)
+    _check(lib, lib.gi_mamba2_gate_norm(out.data_ptr(), _dt(out, "normed rows"), y.data_ptr(), proj.data_ptr(),
+                                        _dt(proj, "projected rows"), _rows(proj, "projected rows"), weight.data_ptr(),
+                                        _dt(weight, "norm weight"), n, inner, int(parts), float(eps), _stream()))
+    return out
+
+
+# ------------------------------------------------------------------------------------------------
+# Routed feed-forward.
+def moe_route(h: torch.Tensor, w_router: torch.Tensor, top: int, w_shared_gate: Optional[torch.Tensor] = None):
+    """(ids int32 [tokens, top], weights float32 [tokens, top], shared gate float32 [tokens] or None)."""
+    lib = _bind()
+    _cuda(h, "activations")
+    ldh = _rows(h, "activations")
+    n, width = h.shape
+    experts = w_router.shape[0]
+    if w_router.dim() != 2 or w_router.shape[1] != width or not w_router.is_contiguous():
+        raise KernelError(f"router weights must be contiguous [experts, {width}]")
+    if w_shared_gate is not None and (w_shared_gate.numel() != width or w_shared_gate.dtype != w_router.dtype
+                                      or not w_shared_gate.is_contiguous()):
+        raise KernelError(f"the shared expert's gate must be {width} values of the router's type")
+    ids = torch.empty((n, top), dtype=torch.int32, device=h.device)
+    wts = torch.empty((n, top), dtype=torch.float32, device=h.device)
+    sg = torch.empty((n,), dtype=torch.float32, device=h.device) if w_shared_gate is not None else None
+    _check(lib, lib.gi_moe_route(ids.data_ptr(), wts.data_ptr(), sg.data_ptr() if sg is not None else None, h.data_ptr(),
+                                 _dt(h, "activations"), ldh, w_router.data_ptr(),
+                                 w_shared_gate.data_ptr() if w_shared_gate is not None else None,
+                                 _dt(w_router, "router weights"), n, width, experts, int(top), _stream()))
+    return ids, wts, sg
+
+
+def moe_plan(ids: torch.Tensor, experts: int):
+    """(offsets int32 [experts + 1], perm int32 [entries], inv int32 [entries]) of the stable sort of `ids` by expert."""
+    lib = _bind()
+    entries = ids.numel()
+    dev = ids.device
+    offsets = torch.empty((experts + 1,), dtype=torch.int32, device=dev)
+    perm = torch.empty((entries,), dtype=torch.int32, device=dev)
+    inv = torch.empty((entries,), dtype=torch.int32, device=dev)
+    scratch = torch.empty(((entries + 1023) // 1024 * experts + entries,), dtype=torch.int32, device=dev)
+    _check(lib, lib.gi_moe_plan(offsets.data_ptr(), perm.data_ptr(), inv.data_ptr(), scratch.data_ptr(), _i32(ids, "expert ids"),
+                                entries, int(experts), _stream()), 3)
+    return offsets, perm, inv
+
+
+def moe_experts(h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, offsets: torch.Tensor, perm: torch.Tensor,
+                top: int) -> torch.Tensor:
+    """Every chosen expert's output, float32 [entries (in sorted order), width]: down_e(silu(gate_e h) * (up_e h)).
+    `w_gate_up` [experts, 2 f, width] (gate rows, then up rows), `w_down` [experts, width, f]."""
+    lib = _bind()
+    _cuda(h, "activations")
+    lda = _rows(h, "activations")
+    experts, f2, width = w_gate_up.shape
+    f = f2 // 2
+    if h.shape[1] != width or tuple(w_down.shape) != (experts, width, f) or not w_gate_up.is_contiguous() or not w_down.is_contiguous():
+        raise KernelError(f"expert weights {tuple(w_gate_up.shape)} and {tuple(w_down.shape)} do not fit rows of {h.shape[1]}")
+    if w_gate_up.dtype != w_down.dtype:
+        raise KernelError("expert weights must share a type")
+    entries = perm.numel()
+    inter = torch.empty((entries, f), dtype=h.dtype, device=h.device)
+    _check(lib, lib.gi_moe_gemm_gate_up(inter.data_ptr(), _dt(h, "activations"), h.data_ptr(), lda, w_gate_up.data_ptr(),
+                                        _dt(w_gate_up, "expert weights"), w_gate_up.stride(0), _i32(offsets, "offsets"),
+                                        _i32(perm, "permutation"), entries, int(top), experts, f, width, _stream()))
+    down = torch.empty((entries, width), dtype=torch.float32, device=h.device)
+    _check(lib, lib.gi_moe_gemm_down(down.data_ptr(), inter.data_ptr(), _dt(inter, "activations"), f, w_down.data_ptr(),
+                                     _dt(w_down, "expert weights"), w_down.stride(0), _i32(offsets, "offsets"), entries,
+                                     experts, width, f, _stream()))
+    return down
+
+
+def moe_combine(residual: torch.Tensor, down: torch.Tensor, inv: torch.Tensor, wts: torch.Tensor,
+                shared: Optional[torch.Tensor] = None, shared_gate: Optional[torch.Tensor] = None) -> None:
+    """residual[t] += sum_k wts[t, k] * down[inv[t, k]] (+ shared_gate[t] * shared[t])."""
+    lib = _bind()
+    _cuda(residual, "residual stream")
+    n, width = residual.shape
+    top = wts.shape[1]
+    if residual.dtype != torch.float32 or not residual.is_contiguous() or down.dtype != torch.float32 or down.shape[1] != width:
+        raise KernelError("expert combine: float32 rows of the stream's width are wanted")
+    if shared is not None and (shared.dtype != torch.float32 or tuple(shared.shape) != (n, width) or not shared.is_contiguous()
+                               or shared_gate is None):
+        raise KernelError("expert combine: the shared expert's output must be float32 [tokens, width] with its gate")
+    _check(lib, lib.gi_moe_combine(residual.data_ptr(), down.data_ptr(), _i32(inv, "inverse permutation"), wts.data_ptr(),
+                                   shared.data_ptr() if shared is not None else None,
+                                   shared_gate.data_ptr() if shared is not None else None, n, width, top, _stream()))

@@ -19,6 +19,8 @@ class PreNormResidual(Block):
         h = self.mixer_norm.forward(x)
         with ops.defer_into(x):
             self.mixer.forward(h, x, step, memory)
+        if self.ffn is None:          # a layer without a feed-forward: the mixer alone
+            return
         if x.is_cuda and not getattr(self.ffn_norm, "settles_pending", False):
             ops.settle(x)
         h = self.ffn_norm.forward(x)

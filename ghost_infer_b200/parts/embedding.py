@@ -1,6 +1,6 @@
 """Token embedding and output head.
 
-x[t] = E[token_t] without scaling (src/model.rs:987-990); logits = W normed with no bias, no cap, no
+x[t] = E[token_t] (src/model.rs:987-990), times `scale` where a model names one; logits = W normed with no bias, no cap, no
 scaling, where W is the embedding table when the model ties them (src/model.rs:637-638, :1183-1186).
 """
 from __future__ import annotations
@@ -21,6 +21,7 @@ class TokenEmbedding(Part):
         super().__init__(params, prefix)
         self.vocab = int(params["vocab_size"])
         self.hidden = int(params["hidden_size"])
+        self.scale = float(params.get("scale", 1.0))
 
     def weights(self) -> List[WeightSpec]:
         return [WeightSpec(self.tensor_name("weight", "weight"), (self.vocab, self.hidden))]
@@ -31,7 +32,7 @@ class TokenEmbedding(Part):
 
     def forward(self, tokens: torch.Tensor) -> torch.Tensor:
         with ops.bucket("embed"):
-            return ops.embed(self.weight, tokens)
+            return ops.embed(self.weight, tokens, scale=self.scale)
 
 
 @register("head", "linear_head")

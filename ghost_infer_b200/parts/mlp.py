@@ -5,6 +5,9 @@ path packs them (src/quant.rs:1135-1154, src/model.rs:1133-1147, src/cuda.rs:923
 
 Tensor names: prefix + "mlp.{gate,up,down}_proj.weight" unless `params["tensor_names"]` gives others for the
 keys "gate", "up", "down".
+
+The same layer with another activation in place of silu (`params["activation"]`: "silu", the default, or
+"gelu_tanh", 0.5 g (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3)))) is registered as "gated_mlp".
 """
 from __future__ import annotations
 
@@ -18,12 +21,16 @@ from .linear import linear
 from .registry import register
 
 
+@register("feed_forward", "gated_mlp")
 @register("feed_forward", "swiglu")
 class SwiGlu(FeedForward):
     def __init__(self, params, prefix=""):
         super().__init__(params, prefix)
         self.hidden = int(params["hidden_size"])
         self.inter = int(params["intermediate_size"])
+        self.activation = str(params.get("activation", "silu"))
+        if self.activation not in ("silu", "gelu_tanh"):
+            raise ValueError(f"unknown activation \"{self.activation}\" (silu, gelu_tanh)")
         self.names = {k: self.tensor_name(k, f"mlp.{k}_proj.weight") for k in ("gate", "up", "down")}
 
     def weights(self) -> List[WeightSpec]:
@@ -39,7 +46,7 @@ class SwiGlu(FeedForward):
         # 16-bit path: gate and up rows interleaved in blocks of 8, so that one block of the decode kernel
         # holds both halves of an activation and applies SwiGLU before anything is written
         self.interleaved = (rt.dtype == torch.bfloat16 and g.dtype == torch.bfloat16 and self.inter % 8 == 0
-                            and rt.device.type == "cuda")
+                            and rt.device.type == "cuda" and self.activation == "silu")
         if self.interleaved:
             blocks = self.inter // 8
             self.w_gate_up = torch.stack([g.view(blocks, 8, self.hidden), u.view(blocks, 8, self.hidden)], dim=1) \
@@ -55,5 +62,5 @@ class SwiGlu(FeedForward):
                 act = ops.swiglu_interleaved(h, self.w_gate_up)
             else:
                 gu = linear(h, self.w_gate_up, out_dtype=self.rt.dtype)
-                act = ops.silu_mul(gu)
+                act = ops.silu_mul(gu) if self.activation == "silu" else ops.act_mul(gu, self.activation)
             linear(act, self.w_down, out=residual, accumulate=True)

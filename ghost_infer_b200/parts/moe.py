@@ -1,0 +1,93 @@
+"""Routed feed-forward: a mixture of small gated feed-forward layers, of which every token uses a few.
+
+Router logits z = W_r h, 32-bit; a token's experts are the `top` largest logits and their weights the softmax over
+those logits alone; expert e computes W_down,e (silu(W_gate,e h) * (W_up,e h)), no biases; the token's output is the
+weighted sum.  A shared expert of the same form (if the model has one) runs for every token and is added, multiplied
+by sigmoid(w_sg . h), one number per token.  residual += all of it.
+
+On the device the (token, choice) entries are sorted by expert without the host learning the counts, so a step's
+launches do not depend on what the router chose and one-token steps can be recorded and replayed.
+
+Tensor names: prefix + "mlp.router", "mlp.e<i>.{gate,up,down}", "mlp.shared.{gate,up,down,sg}" unless
+`params["tensor_names"]` replaces the stems "router", "expert" (a format with `{i}`) or "shared".
+"""
+from __future__ import annotations
+
+from typing import List
+
+import torch
+
+from ..kernels import ops
+from .base import FeedForward, WeightSpec
+from .linear import linear
+from .registry import register
+
+
+@register("feed_forward", "routed_experts")
+class RoutedExperts(FeedForward):
+    def __init__(self, params, prefix=""):
+        super().__init__(params, prefix)
+        self.hidden = int(params["hidden_size"])
+        self.experts = int(params["experts"])
+        self.top = int(params["top"])
+        self.ff = int(params["expert_ff"])
+        self.shared_ff = int(params["shared_ff"]) if params.get("shared_ff") else None
+        if not (1 <= self.top <= self.experts):
+            raise ValueError(f"a token cannot use {self.top} of {self.experts} experts")
+        self.router_name = self.tensor_name("router", "mlp.router")
+        self.expert_stem = self.tensor_name("expert", "mlp.e{i}.")
+        self.shared_stem = self.tensor_name("shared", "mlp.shared.")
+
+    def _expert(self, i: int, what: str) -> str:
+        return self.expert_stem.format(i=i) + what
+
+    def weights(self) -> List[WeightSpec]:
+        out = [WeightSpec(self.router_name, (self.experts, self.hidden))]
+        for i in range(self.experts):
+            out += [WeightSpec(self._expert(i, "gate"), (self.ff, self.hidden)), WeightSpec(self._expert(i, "up"), (self.ff, self.hidden)),
+                    WeightSpec(self._expert(i, "down"), (self.hidden, self.ff))]
+        if self.shared_ff:
+            s = self.shared_stem
+            out += [WeightSpec(s + "gate", (self.shared_ff, self.hidden)), WeightSpec(s + "up", (self.shared_ff, self.hidden)),
+                    WeightSpec(s + "down", (self.hidden, self.shared_ff)), WeightSpec(s + "sg", (1, self.hidden))]
+        return out
+
+    def bind(self, tensors, rt) -> None:
+        super().bind(tensors, rt)
+        self.w_router = rt.place(tensors[self.router_name])
+        gate_up = [torch.cat([tensors[self._expert(i, "gate")], tensors[self._expert(i, "up")]], dim=0) for i in range(self.experts)]
+        self.w_gate_up = rt.place(torch.stack(gate_up))                                   # [E, 2 f, d]: gate rows, then up rows
+        self.w_down = rt.place(torch.stack([tensors[self._expert(i, "down")] for i in range(self.experts)]))   # [E, d, f]
+        if self.w_gate_up.dtype != self.w_down.dtype:
+            self.w_gate_up, self.w_down = self.w_gate_up.float(), self.w_down.float()
+        self.w_sg = None
+        if self.shared_ff:
+            s = self.shared_stem
+            g, u = rt.place(tensors[s + "gate"]), rt.place(tensors[s + "up"])
+            if g.dtype != u.dtype:
+                g, u = g.float(), u.float()
+            f = self.shared_ff
+            self.shared_interleaved = (rt.dtype == torch.bfloat16 and g.dtype == torch.bfloat16 and f % 8 == 0
+                                       and rt.device.type == "cuda")
+            if self.shared_interleaved:
+                self.w_shared_gu = torch.stack([g.view(f // 8, 8, self.hidden), u.view(f // 8, 8, self.hidden)], dim=1) \
+                    .reshape(2 * f, self.hidden).contiguous()
+            else:
+                self.w_shared_gu = torch.cat([g, u], dim=0).contiguous()
+            self.w_shared_down = rt.place(tensors[s + "down"])
+            self.w_sg = rt.place(tensors[s + "sg"]).reshape(-1).to(self.w_router.dtype).contiguous()
+
+    def forward(self, h, residual, step) -> None:
+        with ops.bucket("ffn matmul"):
+            ids, wts, sgate = ops.moe_route(h, self.w_router, self.top, self.w_sg)
+            offsets, perm, inv = ops.moe_plan(ids, self.experts)
+            down = ops.moe_experts(h, self.w_gate_up, self.w_down, offsets, perm, self.top)
+            shared = None
+            if self.shared_ff:
+                if self.shared_interleaved:
+                    act = ops.swiglu_interleaved(h, self.w_shared_gu)
+                else:
+                    act = ops.act_mul(linear(h, self.w_shared_gu, out_dtype=self.rt.dtype), "silu")
+                shared = linear(act, self.w_shared_down, out_dtype=torch.float32)
+            ops.settle(residual)
+            ops.moe_combine(residual, down, inv, wts, shared, sgate)
