@@ -110,6 +110,132 @@ def measure_workload(key, new_tokens=None, clocks=None, no_pdl=False):
     return rec
 
 
+# ---- the hybrid decoder (Barovik) beside the Llama decoder at equal layer sizes ---------------------------------------
+def _barovik(width, heads, kv, dim, vdim, chunk, ff, ssm_heads, ssm_dim, state, groups, experts, top, expert_ff, shared_ff,
+             vocab, pairs):
+    att = {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": vdim, "scale": dim ** -0.5,
+                                          "softcap": 50.0, "mask": {"size": chunk}, "v_mix": True},
+           "mlp": {"kind": "dense", "ff": ff}}
+    ssm = {"type": "mamba2", "mixer": {"heads": ssm_heads, "vdim": ssm_dim, "state": state, "groups": groups, "conv": 4,
+                                       "norm_groups": groups},
+           "mlp": {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": expert_ff}, "shared": {"ff": shared_ff}}}
+    return {"architecture": "Barovik", "width": width, "vocab": vocab, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5},
+            "layers": [att, ssm] * pairs}
+
+
+def _llama_like(width, heads, kv, dim, ff, vocab, layers):
+    return {"architectures": ["LlamaForCausalLM"], "hidden_size": width, "num_hidden_layers": layers, "num_attention_heads": heads,
+            "num_key_value_heads": kv, "head_dim": dim, "intermediate_size": ff, "vocab_size": vocab,
+            "max_position_embeddings": 131072, "rope_theta": 500000.0, "rope_scaling": None, "rms_norm_eps": 1e-5,
+            "tie_word_embeddings": False}
+
+
+# layer sizes of the kind real models have: two pairs of (attention + dense feed-forward, state-space + routed experts)
+HYBRID_SIZES = {
+    "w2048": dict(width=2048, heads=32, kv=8, dim=64, vdim=64, chunk=8192, ff=8192, ssm_heads=64, ssm_dim=64, state=128, groups=8,
+                  experts=16, top=2, expert_ff=2048, shared_ff=2048, vocab=32000, pairs=2),
+    "w4096": dict(width=4096, heads=32, kv=8, dim=128, vdim=128, chunk=8192, ff=14336, ssm_heads=128, ssm_dim=64, state=128, groups=8,
+                  experts=16, top=2, expert_ff=4096, shared_ff=4096, vocab=32000, pairs=2),
+    "w2048_odd": dict(width=2048, heads=32, kv=8, dim=64, vdim=48, chunk=1000, ff=8192, ssm_heads=64, ssm_dim=48, state=96, groups=4,
+                      experts=32, top=4, expert_ff=1024, shared_ff=2048, vocab=32000, pairs=2),
+}
+
+
+def measure_hybrid(args):
+    """`--workload barovik`: prompt and decode throughput of the hybrid decoder at a few real layer sizes (random weights),
+    beside the Llama decoder with the same width, heads, feed-forward width and number of layers; and the device time per
+    kind of operation for one prompt step and one decode step of each.  One JSON line."""
+    import gc
+    import numpy as np
+    import torch
+    import ghost_infer_b200 as gi
+    from ghost_infer_b200.kernels import ops
+    ops.set_pdl(not args.no_pdl)
+    rng = np.random.default_rng(0)
+    prompt_len, batch, held = PROMPT, args.batch, args.held
+    steps, warm = max(8, min(args.steps, 64)), max(3, args.warmup)
+    clocks = ClockSampler()
+    clocks.start()
+    t_begin = time.time()
+    out = {}
+
+    def one(cfg):
+        vocab = cfg.get("vocab", cfg.get("vocab_size"))
+        llm = gi.LLM(cfg, dtype="bfloat16", device="cuda:0", max_tokens=(batch + 1) * (held + 256) + prompt_len + 4096, max_slots=batch + 2,
+                     max_seq_len=held + prompt_len + 512, seed=0)
+        eng, cache = llm.engine, llm.cache
+        prompt = rng.integers(0, vocab, size=prompt_len).tolist()
+
+        def prefill_once():
+            s = cache.open_slot()
+            eng.step([gi.StepEntry(s, prompt, [prompt_len - 1])])
+            cache.close_slot(s)
+
+        for _ in range(3):
+            prefill_once()
+        torch.cuda.synchronize()
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
+        marks[0].record()
+        for i in range(5):
+            prefill_once()
+            marks[i + 1].record()
+        torch.cuda.synchronize()
+        each = sorted(a.elapsed_time(b) for a, b in zip(marks, marks[1:]))
+        pre_ms = each[len(each) // 2]
+        ops.profile_start()
+        prefill_once()
+        pre_buckets = {k: round(v, 3) for k, v in ops.profile_stop().items()}
+        # decode: `batch` sequences that read `held`-token prompts first (a state-space layer's state has to be real)
+        slots = [cache.open_slot() for _ in range(batch)]
+        for s in slots:
+            eng.step([gi.StepEntry(s, rng.integers(0, vocab, size=held).tolist(), [])])
+        runner = eng.decoder(slots)
+        picked = torch.zeros(batch, dtype=torch.int32, device="cuda:0")
+        logits = runner.forward(tokens=rng.integers(0, vocab, size=batch).tolist())
+        for _ in range(warm):
+            ops.sample(logits, 0.0, 0, 1.0, out=picked)
+            logits = runner.forward(dev_tokens=picked)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        l0 = ops.launches
+        a.record()
+        for _ in range(steps):
+            ops.sample(logits, 0.0, 0, 1.0, out=picked)
+            logits = runner.forward(dev_tokens=picked)
+        b.record()
+        torch.cuda.synchronize()
+        dec_ms = a.elapsed_time(b) / steps
+        launches = (ops.launches - l0) // steps
+        ops.profile_start()
+        plain = eng.decoder(slots)             # while profiling a runner launches kernel by kernel
+        for _ in range(4):
+            plain.forward(tokens=rng.integers(0, vocab, size=batch).tolist())
+        dec_buckets = {k: round(v / 4, 4) for k, v in ops.profile_stop().items()}
+        for s in slots:
+            cache.close_slot(s)
+        ops.check_status()
+        rec = {"prefill_tokens_per_s": round(prompt_len * 1000.0 / pre_ms, 1), "prefill_ms": round(pre_ms, 3),
+               "decode_tokens_per_s": round(batch * 1000.0 / dec_ms, 1), "decode_ms_per_step": round(dec_ms, 4),
+               "launches_per_decode_step": int(launches), "prefill_ms_by_kind": pre_buckets, "decode_ms_by_kind": dec_buckets}
+        del llm, eng, cache, runner, plain
+        gc.collect()
+        torch.cuda.empty_cache()
+        return rec
+
+    names = [n for n in HYBRID_SIZES if not args.sizes or n in args.sizes.split(",")]
+    for name in names:
+        z = HYBRID_SIZES[name]
+        hybrid = one(_barovik(**z))
+        llama = one(_llama_like(z["width"], z["heads"], z["kv"], z["dim"], z["ff"], z["vocab"], 2 * z["pairs"]))
+        out[name] = {"sizes": z, "barovik": hybrid, "llama_equal_size": llama}
+    clocks.stop()
+    print(json.dumps({"metric": "Barovik beside the Llama decoder at equal layer sizes: prompt and decode tok/s", "impl": "ours", "n_gpus": 1,
+                      "dtype": "bf16", "data": "synthetic: random N(0, 0.02) weights, uniform random token ids", "prompt_len": prompt_len,
+                      "decode_batch": batch, "decode_held": held, "steps": steps, "warmup": warm, "peaks": peaks(), "results": out,
+                      "clocks": clocks.window(t_begin, time.time())}))
+    return 0
+
+
 def run_workload(key, args):
     """`--workload 1b|3b`: that workload alone, as one JSON line."""
     clocks = ClockSampler()
@@ -243,7 +369,10 @@ def main():
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the named configuration (recorded in config)")
     ap.add_argument("--skip-points", action="store_true")
-    ap.add_argument("--workload", default="8b", choices=["8b", "1b", "3b"], help="8b: the headline; 1b, 3b: the baseline's other workloads")
+    ap.add_argument("--workload", default="8b", choices=["8b", "1b", "3b", "barovik"],
+                    help="8b: the headline; 1b, 3b: the baseline's other workloads; barovik: the hybrid decoder beside the Llama "
+                         "decoder at equal layer sizes (--sizes, --batch, --held)")
+    ap.add_argument("--sizes", default="", help="for --workload barovik: which of its sizes to run, with commas (default: all)")
     ap.add_argument("--tune", default="", help="overrides of kernel choices, e.g. small_skinny=0,attn_waves=2")
     ap.add_argument("--only", default="", choices=["", "prefill", "decode", "timeline"],
                     help="run one phase alone and print its time (a short program for a launch list under a profiler; no bench "
@@ -266,6 +395,8 @@ def main():
         for kv in filter(None, args.tune.split(",")):
             k, v = kv.split("=")
             _ops.TUNE[k] = type(_ops.TUNE[k])(float(v))
+    if args.workload == "barovik":
+        return measure_hybrid(args)
     if args.workload != "8b":
         return run_workload(args.workload, args)
     W = max(3, args.warmup)

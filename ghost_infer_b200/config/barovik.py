@@ -174,13 +174,18 @@ def build_barovik_spec(cfg: BarovikConfig) -> ModelSpec:
     bare = {"tensor_names": {"weight": ""}}      # "l0.norm1", "embed", "head": the tensor is the prefix itself
     norm = PartSpec("rmsnorm", {"size": cfg.width, "eps": cfg.norm_eps, **bare})
     layers = []
+    ignorable = []          # tensors a file may hold for what this model's configuration switches off
     seen_blend = False
     for i, layer in enumerate(cfg.layers):
         m = layer.mixer
+        if layer.mlp is None:
+            ignorable.append(f"l{i}.norm2")
         if layer.type == "attention":
             role = None
             if m.v_mix:
                 role, seen_blend = ("blend" if seen_blend else "source"), True
+            else:
+                ignorable.append(f"l{i}.mix.vmix")
             mixer = PartSpec("sink_attention", {
                 "hidden_size": cfg.width, "num_heads": m.heads, "num_kv_heads": m.kv_heads, "head_dim": m.dim,
                 "v_head_dim": m.vdim, "scale": m.scale, "softcap": m.softcap, "sink": True, "chunk": m.chunk,
@@ -205,6 +210,7 @@ def build_barovik_spec(cfg: BarovikConfig) -> ModelSpec:
         embedding=PartSpec("token_embedding", {"vocab_size": cfg.vocab, "hidden_size": cfg.width, "scale": cfg.embedding_scale, **bare}),
         layers=tuple(layers), schedule=tuple(ScheduleEntry(i) for i in range(len(layers))), final_norm=norm,
         head=PartSpec("linear_head", {"vocab_size": cfg.vocab, "hidden_size": cfg.width, "tied": False, **bare}),
-        stop_token_ids=cfg.stop_token_ids, embedding_prefix="embed", final_norm_prefix="final.norm", head_prefix="head")
+        stop_token_ids=cfg.stop_token_ids, embedding_prefix="embed", final_norm_prefix="final.norm", head_prefix="head",
+        ignorable_tensors=tuple(ignorable))
     spec.validate()
     return spec

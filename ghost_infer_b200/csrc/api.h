@@ -116,6 +116,8 @@ int gi_gemm_generic(void* out, int out_dtype, int mode, const void* A, int a_dty
 #define GI_SKINNY_STORE_F32 1
 #define GI_SKINNY_ACCUM_F32 2   // out (float) += product
 #define GI_SKINNY_SWIGLU 3      // W rows interleaved [8 gate | 8 up]; out[M, N/2] bfloat16 = silu(gate) * up
+#define GI_ACT_GELU 0x100       // or-ed into a gated mode (GI_SKINNY_SWIGLU, GI_TC_SWIGLU) of the tcgen05 products: the gate's
+                                // activation is gelu in its tanh form instead of silu
 #define GI_SKINNY_STORE_DEFER 5 // the same for STORE_BF16: whole tiles are stored, cut tiles stay as partial sums for gi_rope_cache_write
 #define GI_SKINNY_ACCUM_DEFER 4 // gi_gemm_stream_bf16 only: as ACCUM_F32, but tiles cut between blocks leave their partial
                                 // sums in `scratch` for gi_rmsnorm / gi_settle to add (no exchange between blocks)
@@ -200,6 +202,12 @@ int gi_attn_decode_generic_ex(void* out, long ldo, float* part_o, float* part_ml
                               const int* seq_slots, const int* seq_lens, int n_seqs, int n_heads, int n_kv, int hd,
                               float scale, int window, int n_splits, int own_tiles, int hdv, float softcap,
                               const float* sinks, int chunk, void* stream);
+
+// The prompt operation of gi_attn_prefill_generic_ex on tensor cores: bfloat16, key and value sizes multiples of 8 up to 128.
+int gi_attn_prefill_tc_ex(void* out, long ldo, const void* q, long ldq, const void* kcache, const void* vcache,
+                          const int* block_table, int max_pages, const int* cu_seqlens, const int* seq_slots,
+                          const int* seq_pos0, int n_seqs, int max_q_len, int n_heads, int n_kv, int hd, float scale,
+                          int window, int hdv, float softcap, const float* sinks, int chunk, void* stream);
 
 // Keys and values of a step's tokens into the cache without rotation, for packed rows [q: heads * hd | k: kv * hd |
 // v: kv * hdv].  `first` (optional, [tokens, kv * hdv], the rows' type): the values are first blended with it,

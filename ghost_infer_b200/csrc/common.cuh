@@ -69,6 +69,18 @@ __device__ __forceinline__ float silu_mul_bf16(float g, float u) {
   return __fdividef(g, 1.0f + e) * u;
 }
 
+// The same for gelu in its tanh form: 0.5 g (1 + tanh(t)) = g / (1 + e^(-2t)), t = sqrt(2/pi) (g + 0.044715 g^3).
+__device__ __forceinline__ float gelu_tanh_mul_bf16(float g, float u) {
+  const float t2 = 1.5957691216057308f * (g + 0.044715f * g * g * g);      // 2 t
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(t2 * -1.4426950408889634f));
+  return __fdividef(g, 1.0f + e) * u;
+}
+// act 0: silu, 1: gelu (tanh form); for the products' gated epilogues (GI_ACT_GELU in the mode word).
+__device__ __forceinline__ float gated_mul_bf16(float g, float u, int act) {
+  return act ? gelu_tanh_mul_bf16(g, u) : silu_mul_bf16(g, u);
+}
+
 // Four neighbouring values at once (the pointer is aligned to the four of them).
 __device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
 __device__ __forceinline__ float4 ld4(const __nv_bfloat16* p) {

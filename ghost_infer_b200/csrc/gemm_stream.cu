@@ -53,6 +53,7 @@ __device__ int g_stream_status = 0;
 struct Next {
   int N, K, n_ctas, units_ahead, all_shared;
   unsigned long long* timeline;   // this launch's [TL_BLOCKS][TL_EVENTS] stamps, or null
+  int act;                        // this launch's own gated epilogue: 0 silu, 1 gelu (tanh form)
 };
 
 struct Range {
@@ -355,7 +356,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 #pragma unroll
             for (int j = 0; j < GROUP; ++j) {
               const float up = __shfl_down_sync(0xffffffffu, v[m0 + j], 8);
-              h[j] = gi::silu_mul_bf16(v[m0 + j], up);
+              h[j] = gi::gated_mul_bf16(v[m0 + j], up, next.act);
             }
             if (is_gate && f < N) {
 #pragma unroll
@@ -479,6 +480,10 @@ extern "C" int gi_gemm_stream_bf16_ex(void* out, int mode, const void* A, const 
                                       int n_counters, int M, int N, int K, long lda, long ldw, long ldo, int use_pdl,
                                       const void* next_W, int next_N, int next_K, long next_ldw, int next_mode,
                                       int units_ahead, void* stream) {
+  const int act = (mode & GI_ACT_GELU) ? 1 : 0;
+  mode &= 0xff;
+  next_mode &= 0xff;
+  if (act && mode != GI_SKINNY_SWIGLU) return gi::fail(GI_ERR_ARG, "streamed product: an activation without a gated mode");
   if (M <= 0 || N <= 0) return GI_OK;
   if (M > 64) return gi::fail(GI_ERR_UNSUPPORTED, "streamed product: %d rows of activations, at most 64", M);
   if (K <= 0 || K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0)
@@ -496,12 +501,12 @@ extern "C" int gi_gemm_stream_bf16_ex(void* out, int mode, const void* A, const 
   rc = gi::tensor_map_2d(&ma, A, M, K, lda, nt);
   if (rc != GI_OK) return rc;
   // the next product's matrix, if the caller knows it and it can have a tensor map; otherwise nothing is fetched ahead
-  Next next = {0, 0, 0, 0, 0, nullptr};
+  Next next = {0, 0, 0, 0, 0, nullptr, act};
   CUtensorMap mn = mw;
   if (next_W && units_ahead > 0 && next_N > 0 && next_K > 0 && next_K % 8 == 0 && next_ldw % 8 == 0 && !((uintptr_t)next_W & 15) &&
       gi::tensor_map_2d(&mn, next_W, next_N, next_K, next_ldw, TILE_ROWS) == GI_OK) {
     next = {next_N, next_K, grid_for(next_N, next_K, next_mode), units_ahead,
-            (next_mode == GI_SKINNY_ACCUM_DEFER || next_mode == GI_SKINNY_STORE_DEFER) ? 1 : 0, nullptr};
+            (next_mode == GI_SKINNY_ACCUM_DEFER || next_mode == GI_SKINNY_STORE_DEFER) ? 1 : 0, nullptr, act};
   } else {
     mn = mw;
   }

@@ -45,6 +45,7 @@ struct TilePlan {
   int wide_cols;     // column tiles of full width
   int narrow;        // width of the column tiles after them (0: none)
   int n_tiles;       // all tiles
+  int act;           // the gated epilogue's activation: 0 silu, 1 gelu (tanh form)
 };
 
 // What the q/k/v product's epilogue needs to rotate and store by itself (mode GI_TC_QKV_ROPE): the output's columns are
@@ -297,7 +298,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               for (int j = 0; j < 8; j += 2) {
                 const float g0 = __uint_as_float(r[blk * 16 + j]), g1 = __uint_as_float(r[blk * 16 + j + 1]);
                 const float u0 = __uint_as_float(r[blk * 16 + 8 + j]), u1 = __uint_as_float(r[blk * 16 + 8 + j + 1]);
-                __nv_bfloat162 v = __floats2bfloat162_rn(gi::silu_mul_bf16(g0, u0), gi::silu_mul_bf16(g1, u1));
+                __nv_bfloat162 v = __floats2bfloat162_rn(gi::gated_mul_bf16(g0, u0, plan.act), gi::gated_mul_bf16(g1, u1, plan.act));
                 p[j / 2] = *reinterpret_cast<uint32_t*>(&v);
               }
               stage_chunk(stg, row, q * 2 + blk, make_uint4(p[0], p[1], p[2], p[3]));
@@ -421,7 +422,7 @@ int sm_count() {
 // unit) of which one round holds all.
 TilePlan plan_tiles(int M, int N, int bn, int gran, int sms) {
   const int tiles_m = (M + BM - 1) / BM, cols = (N + bn - 1) / bn;
-  TilePlan p = {cols, 0, tiles_m * cols};
+  TilePlan p = {cols, 0, tiles_m * cols, 0};
   const int per_round = sms / tiles_m;                  // column tiles one round of blocks holds
   if (bn != 256 || per_round < 1 || p.n_tiles <= sms || p.n_tiles % sms == 0) return p;
   const int rounds = p.n_tiles / sms;
@@ -472,6 +473,9 @@ int launch_mode(int mode, const CUtensorMap& ma, const CUtensorMap& mw, const CU
 
 extern "C" int gi_gemm_tc_bf16(void* out, int mode, const void* A, const void* W, int M, int N, int K, long lda, long ldw,
                                long ldo, int tile_n, void* stream) {
+  const int act = (mode & GI_ACT_GELU) ? 1 : 0;
+  mode &= 0xff;
+  if (act && mode != GI_TC_SWIGLU) return gi::fail(GI_ERR_ARG, "tensor-core product: an activation without a gated mode");
   if (M <= 0 || N <= 0) return GI_OK;
   if (K <= 0 || K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0)
     return gi::fail(GI_ERR_UNSUPPORTED, "tensor-core product: K (%d) and the row strides (%ld, %ld) must be multiples of 8", K, lda, ldw);
@@ -493,7 +497,8 @@ extern "C" int gi_gemm_tc_bf16(void* out, int mode, const void* A, const void* W
   if (rc != GI_OK) return rc;
   cudaStream_t s = (cudaStream_t)stream;
   const int gran = mode == GI_TC_SWIGLU ? 128 : (mode == GI_TC_STORE_BF16 ? 64 : 32);
-  const TilePlan plan = g_tail_tiles ? plan_tiles(M, N, tile_n, gran, sm_count()) : plan_tiles(M, N, tile_n, gran, 0);
+  TilePlan plan = g_tail_tiles ? plan_tiles(M, N, tile_n, gran, sm_count()) : plan_tiles(M, N, tile_n, gran, 0);
+  plan.act = act;
   CUtensorMap mw2 = mw;
   if (plan.narrow > 0) {
     rc = gi::tensor_map_2d(&mw2, W, N, K, ldw, plan.narrow);

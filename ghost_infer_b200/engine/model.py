@@ -89,7 +89,8 @@ class Model:
         return out
 
     def ignorable_tensors(self) -> List[str]:
-        return list(self.head.ignorable()) if hasattr(self.head, "ignorable") else []
+        out = list(self.head.ignorable()) if hasattr(self.head, "ignorable") else []
+        return out + list(getattr(self.spec, "ignorable_tensors", ()))
 
     def bind(self, tensors: Mapping[str, torch.Tensor], dtype, device="cuda") -> "Model":
         self.rt = Runtime(torch.device(device), _dtype_of(dtype))

@@ -72,6 +72,7 @@ def _bind():
         "gi_act_mul": [P, P, I, I, I, I, I, P],
         "gi_attn_prefill_generic_ex": [P, L, P, L, I, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, F, P, I, P],
         "gi_attn_decode_generic_ex": [P, L, P, P, P, L, I, P, P, P, I, P, P, I, I, I, I, F, I, I, I, I, F, P, I, P],
+        "gi_attn_prefill_tc_ex": [P, L, P, L, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, F, P, I, P],
         "gi_kv_store": [P, I, L, P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, P],
         "gi_mamba2_conv": [P, P, I, L, P, P, I, P, L, I, P, P, I, I, I, I, I, I, P],
         "gi_mamba2_conv_update": [P, I, L, P, L, I, P, P, I, I, I, I, I, P],
@@ -444,6 +445,7 @@ def gemm_generic(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor
 
 
 SKINNY_STORE_BF16, SKINNY_STORE_F32, SKINNY_ACCUM_F32, SKINNY_SWIGLU, SKINNY_ACCUM_DEFER, SKINNY_STORE_DEFER = 0, 1, 2, 3, 4, 5
+ACT_GELU = 0x100        # or-ed into SKINNY_SWIGLU: the gate's activation is gelu (tanh form) instead of silu
 SKINNY_MAX_ROWS = 64
 
 
@@ -467,8 +469,8 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, mode: int, out: Optional[torch
     n, kw = w.shape
     if k != kw:
         raise KernelError(f"matrix product: activations are {k} wide, the weights take {kw}")
-    cols = n // 2 if mode == SKINNY_SWIGLU else n
-    want = {SKINNY_STORE_BF16: torch.bfloat16, SKINNY_SWIGLU: torch.bfloat16}.get(mode, torch.float32)
+    cols = n // 2 if (mode & 0xff) == SKINNY_SWIGLU else n
+    want = {SKINNY_STORE_BF16: torch.bfloat16, SKINNY_SWIGLU: torch.bfloat16}.get(mode & 0xff, torch.float32)
     if out is None:
         if mode == SKINNY_ACCUM_F32:
             raise KernelError("matrix product: accumulation needs an output to add to")
@@ -483,7 +485,8 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, mode: int, out: Optional[torch
 # Choices measured on a B200; benchmarks may override them to try alternatives.
 TUNE = {"small_skinny": False, "attn_waves": 1.0, "attn_tile_keys": 16, "defer_residual": True, "attn_prefill_tcgen05": True, "prefetch_units": 16,
         "attn_merge_inside": False, "attn_own_slices": False, "attn_stages_hd64": 2, "attn_stages_hd128": 3, "attn_rope_inside": False, "stream_whole_percent": 80,
-        "attn_keys_on_rows": True, "attn_kr_warps": 6, "attn_kr_stages": 2, "qkv_rope_epilogue": True, "attn_min_slice": 256}
+        "attn_keys_on_rows": True, "attn_kr_warps": 6, "attn_kr_stages": 2, "qkv_rope_epilogue": True, "attn_min_slice": 256,
+        "attn_general_tc": True}
 USE_STREAM = True    # decode products through the persistent stream-K kernel (else the mma.sync kernel)
 
 
@@ -531,8 +534,8 @@ def gemm_stream(a: torch.Tensor, w: torch.Tensor, mode: int, out: Optional[torch
     n, kw = w.shape
     if k != kw:
         raise KernelError(f"matrix product: activations are {k} wide, the weights take {kw}")
-    cols = n // 2 if mode == SKINNY_SWIGLU else n
-    want = {SKINNY_STORE_BF16: torch.bfloat16, SKINNY_SWIGLU: torch.bfloat16}.get(mode, torch.float32)
+    cols = n // 2 if (mode & 0xff) == SKINNY_SWIGLU else n
+    want = {SKINNY_STORE_BF16: torch.bfloat16, SKINNY_SWIGLU: torch.bfloat16}.get(mode & 0xff, torch.float32)
     if out is None:
         if mode == SKINNY_ACCUM_F32:
             raise KernelError("matrix product: accumulation needs an output to add to")
@@ -658,8 +661,8 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, mode: int, out: Optional[torch.Ten
     n, kw = w.shape
     if k != kw:
         raise KernelError(f"matrix product: activations are {k} wide, the weights take {kw}")
-    cols = n // 2 if mode == SKINNY_SWIGLU else n
-    want = {SKINNY_STORE_BF16: torch.bfloat16, SKINNY_SWIGLU: torch.bfloat16}.get(mode, torch.float32)
+    cols = n // 2 if (mode & 0xff) == SKINNY_SWIGLU else n
+    want = {SKINNY_STORE_BF16: torch.bfloat16, SKINNY_SWIGLU: torch.bfloat16}.get(mode & 0xff, torch.float32)
     if out is None:
         if mode == SKINNY_ACCUM_F32:
             raise KernelError("matrix product: accumulation needs an output to add to")
@@ -1041,14 +1044,19 @@ def linear(h: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = No
     return gemm_generic(h, w, out=out, out_dtype=out_dtype, accumulate=accumulate)
 
 
-def swiglu_interleaved(h: torch.Tensor, w_interleaved: torch.Tensor) -> torch.Tensor:
-    """silu(Wgate h) * (Wup h) where `w_interleaved` holds gate and up rows in blocks [8 gate | 8 up]."""
-    if skinny_ok(h, w_interleaved):
-        return _decode_product(h, w_interleaved, SKINNY_SWIGLU, None)
-    if tc_ok(h, w_interleaved) and w_interleaved.shape[0] % 16 == 0:
-        return gemm_tc(h, w_interleaved, SKINNY_SWIGLU)
+def swiglu_interleaved(h: torch.Tensor, w_interleaved: torch.Tensor, act: str = "silu") -> torch.Tensor:
+    """act(Wgate h) * (Wup h) where `w_interleaved` holds gate and up rows in blocks [8 gate | 8 up]; `act` "silu" or
+    "gelu_tanh" (in the products' epilogues, or as a step of its own where no such product takes the operands)."""
+    mode = SKINNY_SWIGLU | (ACT_GELU if act == "gelu_tanh" else 0)
+    if act not in ("silu", "gelu_tanh"):
+        raise KernelError(f"unknown activation \"{act}\" (silu, gelu_tanh)")
+    if skinny_ok(h, w_interleaved) and USE_STREAM and (w_interleaved.shape[0] + 127) // 128 <= _STREAM_COUNTERS and not (
+            TUNE["small_skinny"] and act != "silu"):
+        return _decode_product(h, w_interleaved, mode, None)
+    if tc_ok(h, w_interleaved) and w_interleaved.shape[0] % 16 == 0 and h.shape[0] > SKINNY_MAX_ROWS:
+        return gemm_tc(h, w_interleaved, mode)
     gu = linear(h, w_interleaved, out_dtype=h.dtype)
-    return silu_mul(gu, interleaved=True)
+    return act_mul(gu, act, interleaved=True)
 
 
 def attn_decode_stages(head_dim: int) -> int:
@@ -1261,8 +1269,35 @@ def attention_general(qkv: torch.Tensor, memory, step, n_heads: int, n_kv: int, 
         return attn_decode_generic(qkv, memory.k, memory.v, memory.block_table, step.seq_slots, step.seq_lens, step.n_seqs,
                                    n_heads, n_kv, head_dim, scale, window, n_splits, out, part_o, part_ml, own_tiles=own_tiles,
                                    **opts)
+    if (TUNE["attn_general_tc"] and qkv.dtype == torch.bfloat16 and memory.k.dtype == torch.bfloat16 and head_dim % 8 == 0
+            and v_dim % 8 == 0 and head_dim <= 128 and v_dim <= 128 and qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0
+            and out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0):
+        return attn_prefill_tc_general(qkv, memory.k, memory.v, memory.block_table, step.cu_seqlens, step.seq_slots,
+                                       step.seq_pos0, step.n_seqs, step.max_q_len, n_heads, n_kv, head_dim, scale, window, out,
+                                       **opts)
     return attn_prefill_generic(qkv, memory.k, memory.v, memory.block_table, step.cu_seqlens, step.seq_slots, step.seq_pos0,
                                 step.n_seqs, step.max_q_len, n_heads, n_kv, head_dim, scale, window, out, **opts)
+
+
+def attn_prefill_tc_general(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_table: torch.Tensor,
+                            cu_seqlens: torch.Tensor, seq_slots: torch.Tensor, seq_pos0: torch.Tensor, n_seqs: int,
+                            max_q_len: int, n_heads: int, n_kv: int, head_dim: int, scale: float, window: Optional[int],
+                            out: torch.Tensor, *, v_dim: Optional[int] = None, softcap: float = 0.0,
+                            sinks: Optional[torch.Tensor] = None, chunk: Optional[int] = None) -> torch.Tensor:
+    """`attn_prefill_generic` with its options on tensor cores: bfloat16, key and value sizes multiples of 8 up to 128."""
+    lib = _bind()
+    _cuda(q, "queries")
+    ldq, ldo = _rows(q, "queries"), _rows(out, "attention output")
+    if q.dtype != torch.bfloat16 or kcache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("the tensor-core prefill attention takes bfloat16 queries, cache and output")
+    if not kcache.is_contiguous() or not vcache.is_contiguous():
+        raise KernelError("the tensor-core prefill attention takes contiguous cache pages")
+    _check(lib, lib.gi_attn_prefill_tc_ex(
+        out.data_ptr(), ldo, q.data_ptr(), ldq, kcache.data_ptr(), vcache.data_ptr(), _i32(block_table, "block table"),
+        block_table.shape[1], _i32(cu_seqlens, "cu_seqlens"), _i32(seq_slots, "slots"), _i32(seq_pos0, "start positions"),
+        n_seqs, max_q_len, n_heads, n_kv, head_dim, float(scale), int(window or 0), int(v_dim or head_dim),
+        float(softcap or 0.0), _sinks_ptr(sinks, n_heads), int(chunk or 0), _stream()))
+    return out
 
 
 def attn_general_decode_plan(n_seqs: int, max_kv_len: int, sm_count: int, n_heads: int, n_kv: int, window: Optional[int],

@@ -46,7 +46,7 @@ class SwiGlu(FeedForward):
         # 16-bit path: gate and up rows interleaved in blocks of 8, so that one block of the decode kernel
         # holds both halves of an activation and applies SwiGLU before anything is written
         self.interleaved = (rt.dtype == torch.bfloat16 and g.dtype == torch.bfloat16 and self.inter % 8 == 0
-                            and rt.device.type == "cuda" and self.activation == "silu")
+                            and rt.device.type == "cuda")
         if self.interleaved:
             blocks = self.inter // 8
             self.w_gate_up = torch.stack([g.view(blocks, 8, self.hidden), u.view(blocks, 8, self.hidden)], dim=1) \
@@ -59,7 +59,7 @@ class SwiGlu(FeedForward):
     def forward(self, h, residual, step) -> None:
         with ops.bucket("ffn matmul"):
             if self.interleaved:
-                act = ops.swiglu_interleaved(h, self.w_gate_up)
+                act = ops.swiglu_interleaved(h, self.w_gate_up, self.activation)
             else:
                 gu = linear(h, self.w_gate_up, out_dtype=self.rt.dtype)
                 act = ops.silu_mul(gu) if self.activation == "silu" else ops.act_mul(gu, self.activation)

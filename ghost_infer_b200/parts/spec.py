@@ -81,6 +81,7 @@ class ModelSpec:
     embedding_prefix: str = "model.embed_tokens."
     final_norm_prefix: str = "model.norm."
     head_prefix: str = "lm_head."
+    ignorable_tensors: Tuple[str, ...] = ()     # names a weights file may carry although no part uses them
 
     def validate(self) -> None:
         for i, e in enumerate(self.schedule):

@@ -253,7 +253,9 @@ def random_weights(cfg, seed=0, dtype=np.float64):
         if layer["type"] == "attention":
             H, G, dk, dv = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
             put(p + "mix.q", (H * dk, d)); put(p + "mix.k", (G * dk, d)); put(p + "mix.v", (G * dv, d))
-            put(p + "mix.vmix", (), 0.2, 0.4); put(p + "mix.sink", (H,), 1.0); put(p + "mix.o", (d, H * dv))
+            put(p + "mix.sink", (H,), 1.0); put(p + "mix.o", (d, H * dv))
+            if m.get("v_mix"):
+                put(p + "mix.vmix", (), 0.2, 0.4)
         else:
             heads, P, N, G, K = int(m["heads"]), int(m["vdim"]), int(m["state"]), int(m["groups"]), int(m["conv"])
             inner, ch = heads * P, heads * P + 2 * G * N
