@@ -226,8 +226,9 @@ def measure_hybrid(args):
     for name in names:
         z = HYBRID_SIZES[name]
         hybrid = one(_barovik(**z))
-        llama = one(_llama_like(z["width"], z["heads"], z["kv"], z["dim"], z["ff"], z["vocab"], 2 * z["pairs"]))
-        out[name] = {"sizes": z, "barovik": hybrid, "llama_equal_size": llama}
+        out[name] = {"sizes": z, "barovik": hybrid}
+        if not args.skip_points:
+            out[name]["llama_equal_size"] = one(_llama_like(z["width"], z["heads"], z["kv"], z["dim"], z["ff"], z["vocab"], 2 * z["pairs"]))
     clocks.stop()
     print(json.dumps({"metric": "Barovik beside the Llama decoder at equal layer sizes: prompt and decode tok/s", "impl": "ours", "n_gpus": 1,
                       "dtype": "bf16", "data": "synthetic: random N(0, 0.02) weights, uniform random token ids", "prompt_len": prompt_len,

@@ -209,6 +209,13 @@ int gi_attn_prefill_tc_ex(void* out, long ldo, const void* q, long ldq, const vo
                           const int* seq_pos0, int n_seqs, int max_q_len, int n_heads, int n_kv, int hd, float scale,
                           int window, int hdv, float softcap, const float* sinks, int chunk, void* stream);
 
+// The one-token operation of gi_attn_decode_generic_ex on tensor cores (keys on the rows of the tile): bfloat16, key and
+// value sizes multiples of 8 up to 128; own_tiles counts tiles of 16 keys.
+int gi_attn_decode_kr_ex(void* out, long ldo, float* part_o, float* part_ml, const void* q, long ldq, const void* kcache,
+                         const void* vcache, const int* block_table, int max_pages, const int* seq_slots, const int* seq_lens,
+                         int n_seqs, int n_heads, int n_kv, int hd, float scale, int window, int n_splits, int own_tiles,
+                         int hdv, float softcap, const float* sinks, int chunk, void* stream);
+
 // Keys and values of a step's tokens into the cache without rotation, for packed rows [q: heads * hd | k: kv * hd |
 // v: kv * hdv].  `first` (optional, [tokens, kv * hdv], the rows' type): the values are first blended with it,
 // v <- (1 - lambda) v + lambda first, in 32-bit, lambda read from device memory; the blended values are also
@@ -257,7 +264,10 @@ int gi_moe_plan(int* offsets, int* perm, int* inv, int* scratch, const int* ids,
 // down: out[r, :] = a[r] W^T stored as float.
 int gi_moe_gemm_gate_up(void* out, int dtype, const void* a, long lda, const void* w, int w_dtype, long w_stride,
                         const int* offsets, const int* perm, int entries, int top, int experts, int f, int k,
-                        void* stream);
+                        int interleaved, void* stream);    // interleaved: W's rows in blocks [8 gate | 8 up]
+// out[r, :] = in[perm[r] / top, :] (the step's rows in sorted order, an expert's rows side by side).
+int gi_moe_gather_rows(void* out, const void* in, int dtype, long ld_in, const int* perm, int entries, int top, int width,
+                       void* stream);
 int gi_moe_gemm_down(float* out, const void* a, int dtype, long lda, const void* w, int w_dtype, long w_stride,
                      const int* offsets, int entries, int experts, int n, int k, void* stream);
 // residual[t, :] += sum_k wts[t, k] * down[inv[t * top + k], :] (k in order) + sgate[t] * shared[t, :] (if given).

@@ -5,9 +5,9 @@
 //           Inputs before a step's first token come from the sequence's state (zeros for a fresh sequence).
 //  * scan:  dt <- softplus(dt + dt_bias); per head (head h reads group h / (heads / G) of B and C)
 //           S <- exp(-exp(A_log) dt) S + dt B x^T   (S is N x P),   y = S^T C + D x.
-//           Everything here is 32-bit; the tokens of a sequence are walked in order, sixteen at a time through shared
-//           memory; a thread owns one column p of S and a run of its rows n, kept in registers across the step.
-//           One token or a thousand take the same arithmetic in the same order, so cutting a prompt changes no bit.
+//           Everything here is 32-bit; the tokens of a sequence are walked in order, thirty-two at a time through shared
+//           memory; a warp owns four columns p of S, its lanes the rows n, kept in registers across the step.
+//           One token or a thousand, alone or in a batch, take the same arithmetic in the same order: no bit changes.
 //  * gate + norm: y * silu(z), divided by the root mean square of each of `parts` equal parts, times a weight.
 // Per-sequence state: one float row per slot, [S: heads * N * P | last taps - 1 conv inputs: (taps - 1) * channels];
 // slot -1 (a padding row of a fixed-size launch) uses the last row of the matrix.
@@ -18,12 +18,11 @@
 
 namespace {
 
-constexpr int CH = 16;   // tokens per trip through shared memory in the scan
 
 __device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
 __device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log1pf(expf(v)); }
 
-// grid (token tiles of 8, sequences); threads walk channels
+// grid (token tiles of 8, sequences, channel tiles of 256): a thread takes one channel of eight tokens
 template <typename T, typename TW>
 __global__ void __launch_bounds__(256)
 conv_kernel(T* __restrict__ out, const T* __restrict__ proj, long ld_proj, const TW* __restrict__ w,
@@ -38,7 +37,8 @@ conv_kernel(T* __restrict__ out, const T* __restrict__ proj, long ld_proj, const
   const int slot = seq_slots[b];
   const float* cs = state + (size_t)(slot >= 0 ? slot : state_rows - 1) * state_ld + s_floats;
   const int n_here = min(8, qlen - i0);
-  for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+  const int c = blockIdx.z * 256 + threadIdx.x;
+  if (c < channels) {
     const float bc = gi::ldf(bias + c);
     for (int ii = 0; ii < n_here; ++ii) {
       const int i = i0 + ii;
@@ -77,81 +77,145 @@ __global__ void conv_update_kernel(const T* __restrict__ proj, long ld_proj, flo
   }
 }
 
-// grid (heads, sequences, column tiles of PT); block PT * NS threads: thread (pl, ns) owns rows ns*NPT.. of column p0+pl
+// grid (heads, sequences, column tiles of SC_W * SC_CPW); a warp owns SC_CPW columns p of the head's state, its lanes the
+// rows (lane l of NPT >= 4 rows owns rows (32 j + l) 4 .. + 3 for j = 0 .. NPT / 4 - 1, so that a warp reads B and C as
+// whole 16-byte words side by side; of fewer rows, l NPT .. + NPT - 1), in registers for the whole step.  Tokens go
+// through shared memory SC_CH at a time (rows past N padded with zeros, which leave their state at zero); B_t and C_t
+// are read once per token for all of a warp's columns.  A token's sum over the rows stays per lane for SC_RB tokens,
+// then the 32 (token, column) sums of a warp are added across its lanes in one halving exchange (31 shuffles instead of
+// 160), after which lane 4 t + c holds token t, column c.  The order of every sum follows from N alone.
+constexpr int SC_W = 4, SC_CPW = 4, SC_COLS = SC_W * SC_CPW, SC_CH = 32, SC_RB = 8;
+
+// One halving step of the exchange: of 2 * HALF values a lane keeps the half its bit `BIT` of the lane number names and
+// adds the other lane's partial sums of the same values.
+template <int HALF, int BIT>
+__device__ __forceinline__ void halve(float (&v)[32], int lane) {
+  const bool upper = (lane & BIT) != 0;
+#pragma unroll
+  for (int k = 0; k < HALF; ++k) {
+    const float send = upper ? v[k] : v[k + HALF];
+    const float keep = upper ? v[k + HALF] : v[k];
+    v[k] = keep + __shfl_xor_sync(0xffffffffu, send, BIT);
+  }
+}
+
 template <typename T, typename TW, int NPT>
-__global__ void scan_kernel(float* __restrict__ y, const T* __restrict__ xbc, const T* __restrict__ proj, long ld_proj,
-                            const TW* __restrict__ dt_bias, const TW* __restrict__ a_log, const TW* __restrict__ d_skip,
-                            float* __restrict__ state, long state_ld, int state_rows,
-                            const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slots, int heads, int P, int N,
-                            int groups, int PT, int NS) {
-  extern __shared__ float sm[];
-  float* sx = sm;                    // [CH][PT]
-  float* sB = sx + CH * PT;          // [CH][N]
-  float* sC = sB + CH * N;           // [CH][N]
-  float* sdt = sC + CH * N;          // [CH]
-  float* sdA = sdt + CH;             // [CH]
-  float* part = sdA + CH;            // [CH][NS][PT]
+__global__ void __launch_bounds__(SC_W * 32)
+scan_kernel(float* __restrict__ y, const T* __restrict__ xbc, const T* __restrict__ proj, long ld_proj,
+            const TW* __restrict__ dt_bias, const TW* __restrict__ a_log, const TW* __restrict__ d_skip,
+            float* __restrict__ state, long state_ld, int state_rows, const int* __restrict__ cu_seqlens,
+            const int* __restrict__ seq_slots, int heads, int P, int N, int groups) {
+  constexpr int NP = 32 * NPT;       // rows with padding
+  extern __shared__ __align__(16) float sm[];
+  float* sB = sm;                    // [SC_CH][NP]
+  float* sC = sB + SC_CH * NP;       // [SC_CH][NP]
+  float* sx = sC + SC_CH * NP;       // [SC_CH][SC_COLS]
+  float* sdt = sx + SC_CH * SC_COLS; // [SC_CH]
+  float* sdA = sdt + SC_CH;          // [SC_CH]
   gi::pdl_prologue();
-  const int h = blockIdx.x, b = blockIdx.y, p0 = blockIdx.z * PT;
+  const int h = blockIdx.x, b = blockIdx.y, p0 = blockIdx.z * SC_COLS;
   const int tok0 = cu_seqlens[b], qlen = cu_seqlens[b + 1] - tok0;
   if (qlen <= 0) return;
   const int slot = seq_slots[b];
   float* S_row = state + (size_t)(slot >= 0 ? slot : state_rows - 1) * state_ld + (size_t)h * N * P;
   const int g = h / (heads / groups);
   const int inner = heads * P, channels = inner + 2 * groups * N;
-  const int tid = threadIdx.x, nthreads = blockDim.x;
-  const int pl = tid % PT, ns = tid / PT, p = p0 + pl, n_lo = ns * NPT;
-  const bool p_ok = p < P;
-  float S[NPT];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int pw = p0 + warp * SC_CPW;             // this warp's first column
+  // row of this lane's i-th value
+  auto row_of = [&](int i) { return NPT >= 4 ? ((i >> 2) * 32 + lane) * 4 + (i & 3) : lane * NPT + i; };
+  float S[SC_CPW][NPT];
 #pragma unroll
-  for (int i = 0; i < NPT; ++i) S[i] = (p_ok && n_lo + i < N) ? S_row[(size_t)(n_lo + i) * P + p] : 0.f;
+  for (int c = 0; c < SC_CPW; ++c)
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) {
+      const int n = row_of(i);
+      S[c][i] = (pw + c < P && n < N) ? S_row[(size_t)n * P + pw + c] : 0.f;
+    }
   const float A = -expf(gi::ldf(a_log + h)), D = gi::ldf(d_skip + h), bias = gi::ldf(dt_bias + h);
 
-  for (int c0 = 0; c0 < qlen; c0 += CH) {
-    const int nc = min(CH, qlen - c0);
+  for (int c0 = 0; c0 < qlen; c0 += SC_CH) {
+    const int nc = min(SC_CH, qlen - c0);
     __syncthreads();
-    for (int idx = tid; idx < nc * PT; idx += nthreads) {
-      const int t = idx / PT, j = idx % PT;
+    for (int idx = tid; idx < nc * NP; idx += SC_W * 32) {
+      const int t = idx / NP, n = idx % NP;
+      float bv = 0.f, cv = 0.f;
+      if (n < N) {
+        const T* r = xbc + (size_t)(tok0 + c0 + t) * channels + inner + (size_t)g * N + n;
+        bv = gi::ldf(r);
+        cv = gi::ldf(r + (size_t)groups * N);
+      }
+      sB[idx] = bv;
+      sC[idx] = cv;
+    }
+    for (int idx = tid; idx < nc * SC_COLS; idx += SC_W * 32) {
+      const int t = idx / SC_COLS, j = idx % SC_COLS;
       sx[idx] = (p0 + j < P) ? gi::ldf(xbc + (size_t)(tok0 + c0 + t) * channels + (size_t)h * P + p0 + j) : 0.f;
     }
-    for (int idx = tid; idx < nc * N; idx += nthreads) {
-      const int t = idx / N, n = idx % N;
-      const T* r = xbc + (size_t)(tok0 + c0 + t) * channels + inner + (size_t)g * N + n;
-      sB[idx] = gi::ldf(r);
-      sC[idx] = gi::ldf(r + (size_t)groups * N);
-    }
-    for (int t = tid; t < nc; t += nthreads) {
+    for (int t = tid; t < nc; t += SC_W * 32) {
       const float dt = softplus_f(gi::ldf(proj + (size_t)(tok0 + c0 + t) * ld_proj + 2 * inner + 2 * groups * N + h) + bias);
       sdt[t] = dt;
       sdA[t] = expf(A * dt);
     }
     __syncthreads();
-    for (int t = 0; t < nc; ++t) {
-      const float dA = sdA[t], dtx = sdt[t] * sx[t * PT + pl];
-      const float* Bt = sB + t * N + n_lo;
-      const float* Ct = sC + t * N + n_lo;
-      float acc = 0.f;
+    for (int t0 = 0; t0 < nc; t0 += SC_RB) {
+      float acc[32];                                  // [SC_RB tokens][SC_CPW columns]
 #pragma unroll
-      for (int i = 0; i < NPT; ++i) {
-        if (n_lo + i < N) {
-          S[i] = fmaf(dA, S[i], dtx * Bt[i]);
-          acc = fmaf(S[i], Ct[i], acc);
+      for (int tl = 0; tl < SC_RB; ++tl) {
+        const int t = t0 + tl;
+#pragma unroll
+        for (int c = 0; c < SC_CPW; ++c) acc[tl * SC_CPW + c] = 0.f;
+        if (t < nc) {                                 // the same for the whole block
+          const float dA = sdA[t], dt = sdt[t];
+          float bv[NPT], cv[NPT];
+          if (NPT >= 4) {
+#pragma unroll
+            for (int j = 0; j < NPT / 4; ++j) {
+              const float4 b4 = *reinterpret_cast<const float4*>(sB + t * NP + (j * 32 + lane) * 4);
+              const float4 c4 = *reinterpret_cast<const float4*>(sC + t * NP + (j * 32 + lane) * 4);
+              bv[4 * j] = b4.x; bv[4 * j + 1] = b4.y; bv[4 * j + 2] = b4.z; bv[4 * j + 3] = b4.w;
+              cv[4 * j] = c4.x; cv[4 * j + 1] = c4.y; cv[4 * j + 2] = c4.z; cv[4 * j + 3] = c4.w;
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < NPT; ++i) {
+              bv[i] = sB[t * NP + lane * NPT + i];
+              cv[i] = sC[t * NP + lane * NPT + i];
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < NPT; ++i) bv[i] *= dt;
+#pragma unroll
+          for (int c = 0; c < SC_CPW; ++c) {
+            const float x = sx[t * SC_COLS + warp * SC_CPW + c];
+            float a = 0.f;
+#pragma unroll
+            for (int i = 0; i < NPT; ++i) {
+              S[c][i] = fmaf(dA, S[c][i], x * bv[i]);
+              a = fmaf(S[c][i], cv[i], a);
+            }
+            acc[tl * SC_CPW + c] = a;
+          }
         }
       }
-      part[(t * NS + ns) * PT + pl] = acc;
-    }
-    __syncthreads();
-    for (int idx = tid; idx < nc * PT; idx += nthreads) {
-      const int t = idx / PT, j = idx % PT;
-      if (p0 + j >= P) continue;
-      float sum = 0.f;
-      for (int s = 0; s < NS; ++s) sum += part[(t * NS + s) * PT + j];
-      y[(size_t)(tok0 + c0 + t) * inner + (size_t)h * P + p0 + j] = sum + D * sx[idx];
+      halve<16, 16>(acc, lane);
+      halve<8, 8>(acc, lane);
+      halve<4, 4>(acc, lane);
+      halve<2, 2>(acc, lane);
+      halve<1, 1>(acc, lane);
+      // lane 4 tl + c now holds token t0 + tl, column c
+      const int t = t0 + (lane >> 2), c = lane & 3;
+      if (t < nc && pw + c < P)
+        y[(size_t)(tok0 + c0 + t) * inner + (size_t)h * P + pw + c] = acc[0] + D * sx[t * SC_COLS + warp * SC_CPW + c];
     }
   }
 #pragma unroll
-  for (int i = 0; i < NPT; ++i)
-    if (p_ok && n_lo + i < N) S_row[(size_t)(n_lo + i) * P + p] = S[i];
+  for (int c = 0; c < SC_CPW; ++c)
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) {
+      const int n = row_of(i);
+      if (pw + c < P && n < N) S_row[(size_t)n * P + pw + c] = S[c][i];
+    }
 }
 
 // grid (tokens, parts)
@@ -176,16 +240,16 @@ gate_norm_kernel(TO* __restrict__ out, const float* __restrict__ y, const T* __r
 }
 
 template <typename T, typename TW, int NPT>
-int launch_scan(dim3 grid, int threads, size_t smem, cudaStream_t s, float* y, const T* xbc, const T* proj, long ld_proj,
-                const TW* dt_bias, const TW* a_log, const TW* d_skip, float* state, long state_ld, int state_rows,
-                const int* cu, const int* slots, int heads, int P, int N, int groups, int PT, int NS) {
+int launch_scan(dim3 grid, size_t smem, cudaStream_t s, float* y, const T* xbc, const T* proj, long ld_proj, const TW* dt_bias,
+                const TW* a_log, const TW* d_skip, float* state, long state_ld, int state_rows, const int* cu, const int* slots,
+                int heads, int P, int N, int groups) {
   auto kern = scan_kernel<T, TW, NPT>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return gi::fail(GI_ERR_CUDA, "mamba2 scan: %s", cudaGetErrorString(e));
   }
-  return gi::check(gi::launch(kern, grid, dim3(threads), smem, s, y, xbc, proj, ld_proj, dt_bias, a_log, d_skip, state,
-                              state_ld, state_rows, cu, slots, heads, P, N, groups, PT, NS), "mamba2 scan");
+  return gi::check(gi::launch(kern, grid, dim3(SC_W * 32), smem, s, y, xbc, proj, ld_proj, dt_bias, a_log, d_skip, state, state_ld,
+                              state_rows, cu, slots, heads, P, N, groups), "mamba2 scan");
 }
 
 }  // namespace
@@ -197,7 +261,8 @@ extern "C" int gi_mamba2_conv(void* xbc_out, const void* proj, int dtype, long l
   if (n_seqs <= 0 || max_q_len <= 0) return GI_OK;
   if (taps < 1 || channels <= 0 || inner <= 0) return gi::fail(GI_ERR_ARG, "mamba2 conv: bad sizes");
   if (n_seqs > 65535) return gi::fail(GI_ERR_UNSUPPORTED, "mamba2 conv: more than 65535 sequences in one launch");
-  dim3 grid((max_q_len + 7) / 8, n_seqs);
+  if ((channels + 255) / 256 > 65535) return gi::fail(GI_ERR_UNSUPPORTED, "mamba2 conv: %d channels are more than one launch takes", channels);
+  dim3 grid((max_q_len + 7) / 8, n_seqs, (channels + 255) / 256);
   cudaError_t e = cudaSuccess;
   GI_DISPATCH_DTYPE(dtype, T, GI_DISPATCH_DTYPE(w_dtype, TW,
       e = gi::launch(conv_kernel<T, TW>, grid, dim3(256), 0, (cudaStream_t)stream, (T*)xbc_out, (const T*)proj, ld_proj,
@@ -227,24 +292,20 @@ extern "C" int gi_mamba2_scan(float* y, const void* xbc, const void* proj, int d
   if (heads <= 0 || P <= 0 || N <= 0 || groups <= 0 || heads % groups != 0)
     return gi::fail(GI_ERR_ARG, "mamba2 scan: %d heads, %d groups, head size %d, state %d", heads, groups, P, N);
   if (n_seqs > 65535 || heads > 65535) return gi::fail(GI_ERR_UNSUPPORTED, "mamba2 scan: more than 65535 sequences or heads");
-  // a block takes up to 64 columns of one head's state; a thread the fewest rows (a power of two, at most 64) for
-  // which the block stays within 256 threads where that is possible
-  const int PT = P < 64 ? P : 64;
+  if (N > 1024) return gi::fail(GI_ERR_UNSUPPORTED, "mamba2 scan: a state of %d rows is more than a warp's lanes take", N);
   int npt = 1;
-  while (npt < 64 && PT * ((N + npt - 1) / npt) > 256) npt *= 2;
-  const int NS = (N + npt - 1) / npt;
-  const int threads = PT * NS;
-  if (threads > 1024) return gi::fail(GI_ERR_UNSUPPORTED, "mamba2 scan: a state of %d rows is more than one block takes", N);
-  dim3 grid(heads, n_seqs, (P + PT - 1) / PT);
-  const size_t smem = ((size_t)CH * PT + 2 * (size_t)CH * N + 2 * CH + (size_t)CH * NS * PT) * sizeof(float);
+  while (32 * npt < N) npt *= 2;
+  dim3 grid(heads, n_seqs, (P + SC_COLS - 1) / SC_COLS);
+  if (grid.z > 65535) return gi::fail(GI_ERR_UNSUPPORTED, "mamba2 scan: head size %d is more than one launch takes", P);
+  const size_t smem = (2 * (size_t)SC_CH * 32 * npt + (size_t)SC_CH * SC_COLS + 2 * SC_CH) * sizeof(float);
   cudaStream_t s = (cudaStream_t)stream;
   int rc = GI_OK;
 #define GI_SCAN_CASE(NPT)                                                                                              \
   case NPT:                                                                                                            \
     GI_DISPATCH_DTYPE(dtype, T, GI_DISPATCH_DTYPE(w_dtype, TW,                                                         \
-        rc = (launch_scan<T, TW, NPT>(grid, threads, smem, s, y, (const T*)xbc, (const T*)proj, ld_proj, (const TW*)dt_bias, \
+        rc = (launch_scan<T, TW, NPT>(grid, smem, s, y, (const T*)xbc, (const T*)proj, ld_proj, (const TW*)dt_bias,    \
                                       (const TW*)a_log, (const TW*)d_skip, state, state_ld, state_rows, cu_seqlens,    \
-                                      seq_slots, heads, P, N, groups, PT, NS))));                                      \
+                                      seq_slots, heads, P, N, groups))));                                              \
     break;
   switch (npt) {
     GI_SCAN_CASE(1)
@@ -253,7 +314,6 @@ extern "C" int gi_mamba2_scan(float* y, const void* xbc, const void* proj, int d
     GI_SCAN_CASE(8)
     GI_SCAN_CASE(16)
     GI_SCAN_CASE(32)
-    GI_SCAN_CASE(64)
   }
 #undef GI_SCAN_CASE
   return rc;

@@ -1,6 +1,6 @@
 // Routed feed-forward (mixture of experts): every token picks `top` of `experts` small gated feed-forward layers.
 //
-//  * route:   logits = h W_r^T in 32-bit (one warp per token, lanes stride the width, a fixed order of additions);
+//  * route:   logits = h W_r^T in 32-bit (one block per token, a warp per expert in turn, a fixed order of additions);
 //             the `top` largest logits (the lower index wins a tie); weights = softmax over the chosen logits only;
 //             optionally a gate for a shared expert, sigmoid(h . w_sg).
 //  * plan:    a stable counting sort of the (token, choice) entries by expert, entirely on the device, so that a step
@@ -21,31 +21,67 @@ namespace {
 
 constexpr int SEG = 1024;
 
+// Sixteen bytes of a row at once, as floats.
+template <typename T> struct Vec16;
+template <> struct Vec16<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void load(const float* p, float (&v)[8]) {
+    const float4 x = *reinterpret_cast<const float4*>(p);
+    v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+  }
+};
+template <> struct Vec16<__nv_bfloat16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 x = *reinterpret_cast<const uint4*>(p);
+    const uint32_t r[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[2 * i] = __uint_as_float(r[i] << 16);
+      v[2 * i + 1] = __uint_as_float(r[i] & 0xffff0000u);
+    }
+  }
+};
+
+// One block per token: the row goes to shared memory as floats once; warp w forms the logits of experts w, w + 4, ...
+// (and the last warp's turn after them the shared expert's gate); then the first warp picks.
 template <typename T, typename TW>
 __global__ void __launch_bounds__(128)
 route_kernel(int* __restrict__ ids, float* __restrict__ wts, float* __restrict__ sgate, const T* __restrict__ h, long ldh,
-             const TW* __restrict__ w_router, const TW* __restrict__ w_sg, int n_tokens, int width, int experts, int top) {
-  extern __shared__ float sm[];            // [4 warps][experts] logits
+             const TW* __restrict__ w_router, const TW* __restrict__ w_sg, int n_tokens, int width, int experts, int top,
+             int vec) {
+  extern __shared__ __align__(16) float sm[];
+  float* hs = sm;                          // [width] (rounded up to a multiple of 8)
+  float* lg = sm + ((width + 7) / 8) * 8;  // [experts]
   gi::pdl_prologue();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * 4 + warp;
-  if (t >= n_tokens) return;
-  float* lg = sm + (size_t)warp * experts;
+  const int t = blockIdx.x;
   const T* hr = h + (size_t)t * ldh;
-  for (int e = 0; e < experts; ++e) {
-    const TW* wr = w_router + (size_t)e * width;
+  for (int i = threadIdx.x; i < width; i += 128) hs[i] = gi::ldf(hr + i);
+  __syncthreads();
+  const int rows = experts + (w_sg != nullptr ? 1 : 0);
+  for (int e = warp; e < rows; e += 4) {
+    const TW* wr = e < experts ? w_router + (size_t)e * width : w_sg;
     float acc = 0.f;
-    for (int i = lane; i < width; i += 32) acc = fmaf(gi::ldf(hr + i), gi::ldf(wr + i), acc);
+    if (vec) {
+      constexpr int VN = Vec16<TW>::N;
+      for (int i = lane * VN; i < width; i += 32 * VN) {
+        float wv[8];
+        Vec16<TW>::load(wr + i, wv);
+#pragma unroll
+        for (int j = 0; j < VN; ++j) acc = fmaf(hs[i + j], wv[j], acc);
+      }
+    } else {
+      for (int i = lane; i < width; i += 32) acc = fmaf(hs[i], gi::ldf(wr + i), acc);
+    }
     acc = gi::warp_sum(acc);
-    if (lane == 0) lg[e] = acc;
+    if (lane == 0) {
+      if (e < experts) lg[e] = acc;
+      else sgate[t] = 1.0f / (1.0f + expf(-acc));
+    }
   }
-  if (w_sg != nullptr) {
-    float acc = 0.f;
-    for (int i = lane; i < width; i += 32) acc = fmaf(gi::ldf(hr + i), gi::ldf(w_sg + i), acc);
-    acc = gi::warp_sum(acc);
-    if (lane == 0) sgate[t] = 1.0f / (1.0f + expf(-acc));
-  }
-  __syncwarp();
+  __syncthreads();
+  if (warp != 0) return;
   float first = 0.f, sum = 0.f, mine = 0.f;      // lane k keeps the k-th chosen logit (top <= 32)
   for (int k = 0; k < top; ++k) {
     float best = -INFINITY;
@@ -157,7 +193,8 @@ __device__ __forceinline__ bool tile_rows(const int* __restrict__ offsets, int e
 template <typename TA, typename TW, bool DUAL>
 __global__ void __launch_bounds__(256)
 expert_gemm_kernel(void* __restrict__ out_, const TA* __restrict__ A, long lda, const TW* __restrict__ W, long w_stride,
-                   const int* __restrict__ offsets, const int* __restrict__ perm, int top, int experts, int N, int K) {
+                   const int* __restrict__ offsets, const int* __restrict__ perm, int top, int experts, int N, int K,
+                   int interleaved) {
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
   __shared__ float Us[DUAL ? BK : 1][BN + 4];
@@ -188,8 +225,11 @@ expert_gemm_kernel(void* __restrict__ out_, const TA* __restrict__ A, long lda, 
       if (k < K) {
         if (src[r] >= 0) a = gi::ldf(A + (size_t)src[r] * lda + k);
         if (n0 + r < N) {
-          w = gi::ldf(We + (size_t)(n0 + r) * K + k);
-          if (DUAL) u = gi::ldf(We + (size_t)(N + n0 + r) * K + k);
+          // gate and up rows of output n: rows n and N + n, or, interleaved in blocks of 8, (n / 8) * 16 + n % 8 and 8 further
+          const int n = n0 + r;
+          const size_t gr = (DUAL && interleaved) ? (size_t)(n / 8) * 16 + n % 8 : (size_t)n;
+          w = gi::ldf(We + gr * K + k);
+          if (DUAL) u = gi::ldf(We + (interleaved ? gr + 8 : (size_t)N + n) * K + k);
         }
       }
       As[kk][r] = a;
@@ -235,6 +275,114 @@ expert_gemm_kernel(void* __restrict__ out_, const TA* __restrict__ A, long lda, 
   }
 }
 
+// ---- the same products for a step of few rows (one-token steps): bound by the bytes of the experts' matrices ----------
+// grid (column tiles of 32, experts); a block stages up to 8 of its expert's rows in shared memory and streams 32 rows
+// of the expert's matrix past them, 16 bytes per lane per load; a warp takes 8 columns, its lanes cut K between them
+// and their sums meet in a fixed order (a lane's own partial sums in k order, then the warp's tree).  An expert without
+// rows leaves at once, so the launch reads only the matrices of experts that were chosen.
+constexpr int GEMV_WARPS = 4, GEMV_COLS = 32, GEMV_ROWS = 8, GEMV_MAX_ENTRIES = 512;
+constexpr int GEMV_CPW = GEMV_COLS / GEMV_WARPS;     // columns per warp
+
+inline bool gemv_ok(int dtype, int w_dtype, int k, const void* a, const void* w, long lda) {
+  const int per = dtype == GI_F32 ? 4 : 8;             // elements per 16-byte load
+  return dtype == w_dtype && k % per == 0 && lda % per == 0 && !(((uintptr_t)a | (uintptr_t)w) & 15) &&
+         (size_t)GEMV_ROWS * k * (dtype == GI_F32 ? 4 : 2) <= 160 * 1024;
+}
+
+template <typename T, bool DUAL>
+__global__ void __launch_bounds__(GEMV_WARPS * 32)
+expert_gemv_kernel(void* __restrict__ out_, const T* __restrict__ A, long lda, const T* __restrict__ W, long w_stride,
+                   const int* __restrict__ offsets, const int* __restrict__ perm, int top, int N, int K, int interleaved) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  T* As = reinterpret_cast<T*>(smem_raw);            // [GEMV_ROWS][K]
+  constexpr int VN = Vec16<T>::N;
+  gi::pdl_prologue();
+  const int e = blockIdx.y;
+  const int lo = offsets[e], hi = offsets[e + 1];
+  if (hi <= lo) return;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const T* We = W + (size_t)e * w_stride;
+  const int n_base = blockIdx.x * GEMV_COLS + warp * GEMV_CPW;
+  for (int r0 = lo; r0 < hi; r0 += GEMV_ROWS) {
+    const int rows = min(GEMV_ROWS, hi - r0);
+    __syncthreads();
+    for (int idx = tid; idx < rows * (K / VN); idx += GEMV_WARPS * 32) {
+      const int r = idx / (K / VN), c = idx % (K / VN);
+      const int src = perm != nullptr ? perm[r0 + r] / top : r0 + r;
+      *reinterpret_cast<uint4*>(As + (size_t)r * K + c * VN) = *reinterpret_cast<const uint4*>(A + (size_t)src * lda + c * VN);
+    }
+    __syncthreads();
+    // four columns at a time, so that a lane has four (eight with the up rows) 16-byte loads in flight per turn
+    for (int j0 = 0; j0 < GEMV_CPW; j0 += 4) {
+      if (n_base + j0 >= N) break;                      // the same for the whole warp
+      const T* wg[4];
+      const T* wu[4];
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) {
+        const int n = min(n_base + j0 + jj, N - 1);     // a column past the end repeats the last one and is not stored
+        const size_t gr = (DUAL && interleaved) ? (size_t)(n / 8) * 16 + n % 8 : (size_t)n;
+        wg[jj] = We + gr * K;
+        wu[jj] = We + (interleaved ? gr + 8 : (size_t)N + n) * K;
+      }
+      float acc[4][GEMV_ROWS], acu[DUAL ? 4 : 1][GEMV_ROWS];
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj)
+#pragma unroll
+        for (int r = 0; r < GEMV_ROWS; ++r) {
+          acc[jj][r] = 0.f;
+          if (DUAL) acu[jj][r] = 0.f;
+        }
+      for (int k = lane * VN; k < K; k += 32 * VN) {
+        float wv[4][8], uv[DUAL ? 4 : 1][8], av[8];
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+          Vec16<T>::load(wg[jj] + k, wv[jj]);
+          if (DUAL) Vec16<T>::load(wu[jj] + k, uv[jj]);
+        }
+#pragma unroll
+        for (int r = 0; r < GEMV_ROWS; ++r) {
+          if (r < rows) {
+            Vec16<T>::load(As + (size_t)r * K + k, av);
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj)
+#pragma unroll
+              for (int i = 0; i < VN; ++i) {
+                acc[jj][r] = fmaf(av[i], wv[jj][i], acc[jj][r]);
+                if (DUAL) acu[jj][r] = fmaf(av[i], uv[jj][i], acu[jj][r]);
+              }
+          }
+        }
+      }
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) {
+        const int n = n_base + j0 + jj;
+#pragma unroll
+        for (int r = 0; r < GEMV_ROWS; ++r) {
+          if (r >= rows) break;
+          const float g = gi::warp_sum(acc[jj][r]);
+          if (DUAL) {
+            const float u = gi::warp_sum(acu[jj][r]);
+            if (lane == 0 && n < N) gi::stf((T*)out_ + (size_t)(r0 + r) * N + n, g / (1.0f + expf(-g)) * u);
+          } else if (lane == 0 && n < N) {
+            ((float*)out_)[(size_t)(r0 + r) * N + n] = g;
+          }
+        }
+      }
+    }
+  }
+}
+
+// out[r, :] = in[idx[r] / top, :]: the rows of a step in the order of the sort, for products that want an expert's rows
+// side by side.
+template <typename T>
+__global__ void gather_rows_kernel(T* __restrict__ out, const T* __restrict__ in, long ld_in, const int* __restrict__ idx,
+                                   int top, int width) {
+  gi::pdl_prologue();
+  const int r = blockIdx.x;
+  const T* src = in + (size_t)(idx[r] / top) * ld_in;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) out[(size_t)r * width + i] = src[i];
+}
+
 __global__ void __launch_bounds__(256)
 combine_kernel(float* __restrict__ residual, const float* __restrict__ down, const int* __restrict__ inv,
                const float* __restrict__ wts, const float* __restrict__ shared, const float* __restrict__ sgate, int width,
@@ -258,14 +406,17 @@ extern "C" int gi_moe_route(int* ids, float* wts, float* sgate, const void* h, i
   if (experts < 1 || top < 1 || top > experts || top > 32 || experts > 8192)
     return gi::fail(GI_ERR_UNSUPPORTED, "router: %d of %d experts (at most 32 of 8192)", top, experts);
   if (w_sg != nullptr && sgate == nullptr) return gi::fail(GI_ERR_ARG, "router: a shared gate needs somewhere to go");
-  const size_t smem = 4 * (size_t)experts * sizeof(float);
+  const size_t smem = (((size_t)width + 7) / 8 * 8 + (size_t)experts) * sizeof(float);
+  if (smem > 200 * 1024) return gi::fail(GI_ERR_UNSUPPORTED, "router: rows of %d values are wider than its shared memory", width);
+  const int per = w_dtype == GI_F32 ? 4 : 8;
+  const int vec = (width % per == 0 && !(((uintptr_t)w_router | (uintptr_t)w_sg) & 15)) ? 1 : 0;
   cudaError_t e = cudaSuccess;
   GI_DISPATCH_DTYPE(dtype, T, GI_DISPATCH_DTYPE(w_dtype, TW, {
       auto kern = route_kernel<T, TW>;
       if (smem > 48 * 1024) e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e == cudaSuccess)
-        e = gi::launch(kern, dim3((n_tokens + 3) / 4), dim3(128), smem, (cudaStream_t)stream, ids, wts, sgate, (const T*)h, ldh,
-                       (const TW*)w_router, (const TW*)w_sg, n_tokens, width, experts, top);
+        e = gi::launch(kern, dim3(n_tokens), dim3(128), smem, (cudaStream_t)stream, ids, wts, sgate, (const T*)h, ldh,
+                       (const TW*)w_router, (const TW*)w_sg, n_tokens, width, experts, top, vec);
   }));
   return gi::check(e, "router");
 }
@@ -291,16 +442,30 @@ extern "C" int gi_moe_plan(int* offsets, int* perm, int* inv, int* scratch, cons
 
 extern "C" int gi_moe_gemm_gate_up(void* out, int dtype, const void* a, long lda, const void* w, int w_dtype, long w_stride,
                                    const int* offsets, const int* perm, int entries, int top, int experts, int f, int k,
-                                   void* stream) {
+                                   int interleaved, void* stream) {
   if (entries <= 0) return GI_OK;
   if (f <= 0 || k <= 0 || top < 1) return gi::fail(GI_ERR_ARG, "expert product: bad sizes");
+  if (interleaved && f % 8 != 0) return gi::fail(GI_ERR_ARG, "expert product: interleaved rows need a width that is a multiple of 8");
+  if (entries <= GEMV_MAX_ENTRIES && gemv_ok(dtype, w_dtype, k, a, w, lda)) {
+    cudaError_t e = cudaSuccess;
+    const size_t smem = (size_t)GEMV_ROWS * k * (dtype == GI_F32 ? 4 : 2);
+    dim3 grid((f + GEMV_COLS - 1) / GEMV_COLS, experts);
+    GI_DISPATCH_DTYPE(dtype, T, {
+        auto kern = expert_gemv_kernel<T, true>;
+        if (smem > 48 * 1024) e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess)
+          e = gi::launch(kern, grid, dim3(GEMV_WARPS * 32), smem, (cudaStream_t)stream, out, (const T*)a, lda, (const T*)w, w_stride,
+                         offsets, perm, top, f, k, interleaved);
+    });
+    return gi::check(e, "expert product (gate, up; few rows)");
+  }
   const long tiles = (entries + BM - 1) / BM + experts;
   if (tiles > 65535) return gi::fail(GI_ERR_UNSUPPORTED, "expert product: %d rows are more than one launch takes", entries);
   dim3 grid((f + BN - 1) / BN, (unsigned)tiles);
   cudaError_t e = cudaSuccess;
   GI_DISPATCH_DTYPE(dtype, TA, GI_DISPATCH_DTYPE(w_dtype, TW,
       e = gi::launch(expert_gemm_kernel<TA, TW, true>, grid, dim3(256), 0, (cudaStream_t)stream, out, (const TA*)a, lda,
-                     (const TW*)w, w_stride, offsets, perm, top, experts, f, k)));
+                     (const TW*)w, w_stride, offsets, perm, top, experts, f, k, interleaved)));
   return gi::check(e, "expert product (gate, up)");
 }
 
@@ -308,13 +473,26 @@ extern "C" int gi_moe_gemm_down(float* out, const void* a, int dtype, long lda, 
                                 const int* offsets, int entries, int experts, int n, int k, void* stream) {
   if (entries <= 0) return GI_OK;
   if (n <= 0 || k <= 0) return gi::fail(GI_ERR_ARG, "expert product: bad sizes");
+  if (entries <= GEMV_MAX_ENTRIES && gemv_ok(dtype, w_dtype, k, a, w, lda)) {
+    cudaError_t e = cudaSuccess;
+    const size_t smem = (size_t)GEMV_ROWS * k * (dtype == GI_F32 ? 4 : 2);
+    dim3 grid((n + GEMV_COLS - 1) / GEMV_COLS, experts);
+    GI_DISPATCH_DTYPE(dtype, T, {
+        auto kern = expert_gemv_kernel<T, false>;
+        if (smem > 48 * 1024) e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess)
+          e = gi::launch(kern, grid, dim3(GEMV_WARPS * 32), smem, (cudaStream_t)stream, (void*)out, (const T*)a, lda, (const T*)w,
+                         w_stride, offsets, (const int*)nullptr, 1, n, k, 0);
+    });
+    return gi::check(e, "expert product (down; few rows)");
+  }
   const long tiles = (entries + BM - 1) / BM + experts;
   if (tiles > 65535) return gi::fail(GI_ERR_UNSUPPORTED, "expert product: %d rows are more than one launch takes", entries);
   dim3 grid((n + BN - 1) / BN, (unsigned)tiles);
   cudaError_t e = cudaSuccess;
   GI_DISPATCH_DTYPE(dtype, TA, GI_DISPATCH_DTYPE(w_dtype, TW,
       e = gi::launch(expert_gemm_kernel<TA, TW, false>, grid, dim3(256), 0, (cudaStream_t)stream, (void*)out, (const TA*)a, lda,
-                     (const TW*)w, w_stride, offsets, (const int*)nullptr, 1, experts, n, k)));
+                     (const TW*)w, w_stride, offsets, (const int*)nullptr, 1, experts, n, k, 0)));
   return gi::check(e, "expert product (down)");
 }
 
@@ -324,4 +502,14 @@ extern "C" int gi_moe_combine(float* residual, const float* down, const int* inv
   if (shared != nullptr && sgate == nullptr) return gi::fail(GI_ERR_ARG, "expert combine: a shared output needs its gate");
   return gi::check(gi::launch(combine_kernel, dim3(n_tokens), dim3(256), 0, (cudaStream_t)stream, residual, down, inv, wts, shared,
                               sgate, width, top), "expert combine");
+}
+
+extern "C" int gi_moe_gather_rows(void* out, const void* in, int dtype, long ld_in, const int* perm, int entries, int top,
+                                  int width, void* stream) {
+  if (entries <= 0) return GI_OK;
+  if (top < 1 || width <= 0) return gi::fail(GI_ERR_ARG, "gather: bad sizes");
+  cudaError_t e = cudaSuccess;
+  GI_DISPATCH_DTYPE(dtype, T, e = gi::launch(gather_rows_kernel<T>, dim3(entries), dim3(256), 0, (cudaStream_t)stream, (T*)out,
+                                             (const T*)in, ld_in, perm, top, width));
+  return gi::check(e, "gather rows");
 }

@@ -73,6 +73,7 @@ def _bind():
         "gi_attn_prefill_generic_ex": [P, L, P, L, I, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, F, P, I, P],
         "gi_attn_decode_generic_ex": [P, L, P, P, P, L, I, P, P, P, I, P, P, I, I, I, I, F, I, I, I, I, F, P, I, P],
         "gi_attn_prefill_tc_ex": [P, L, P, L, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, F, P, I, P],
+        "gi_attn_decode_kr_ex": [P, L, P, P, P, L, P, P, P, I, P, P, I, I, I, I, F, I, I, I, I, F, P, I, P],
         "gi_kv_store": [P, I, L, P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, P],
         "gi_mamba2_conv": [P, P, I, L, P, P, I, P, L, I, P, P, I, I, I, I, I, I, P],
         "gi_mamba2_conv_update": [P, I, L, P, L, I, P, P, I, I, I, I, I, P],
@@ -80,7 +81,8 @@ def _bind():
         "gi_mamba2_gate_norm": [P, I, P, P, I, L, P, I, I, I, I, F, P],
         "gi_moe_route": [P, P, P, P, I, L, P, P, I, I, I, I, I, P],
         "gi_moe_plan": [P, P, P, P, P, I, I, P],
-        "gi_moe_gemm_gate_up": [P, I, P, L, P, I, L, P, P, I, I, I, I, I, P],
+        "gi_moe_gemm_gate_up": [P, I, P, L, P, I, L, P, P, I, I, I, I, I, I, P],
+        "gi_moe_gather_rows": [P, P, I, L, P, I, I, I, P],
         "gi_moe_gemm_down": [P, P, I, L, P, I, L, P, I, I, I, I, P],
         "gi_moe_combine": [P, P, P, P, P, P, I, I, I, P],
     }
@@ -149,7 +151,8 @@ def _i32(t: Optional[torch.Tensor], what: str):
 # pair of CUDA events brackets each such stretch on the launching stream: device time, no synchronisation inside a
 # step.  Steps are then launched kernel by kernel (no graph replay, no dependent launch, which would let one bucket's
 # kernels run inside another's stretch).  Off, `bucket` hands out one shared do-nothing context.
-BUCKETS = ("embed", "norm", "qkv matmul", "rope+cache", "attention", "out matmul", "ffn matmul", "logits", "sampling")
+BUCKETS = ("embed", "norm", "qkv matmul", "rope+cache", "attention", "conv", "scan", "gated norm", "out matmul", "ffn matmul",
+           "router", "experts", "logits", "sampling")
 
 
 class _NoBucket:
@@ -1260,12 +1263,26 @@ def attention_general(qkv: torch.Tensor, memory, step, n_heads: int, n_kv: int, 
     opts = dict(v_dim=v_dim, softcap=softcap, sinks=sinks, chunk=chunk)
     if step.is_decode:
         if plan is None:
-            plan = attn_general_decode_plan(step.n_seqs, step.max_kv_len, step.sm_count, n_heads, n_kv, window, chunk, qkv.dtype)
-        n_splits, own_tiles = plan
+            plan = attn_general_decode_plan(step.n_seqs, step.max_kv_len, step.sm_count, n_heads, n_kv, window, chunk, qkv.dtype,
+                                            head_dim, v_dim)
+        kind, n_splits, own_tiles = plan
         part_o = part_ml = None
         if n_splits > 1:
             part_o = torch.empty((step.n_seqs * n_heads * n_splits * v_dim,), dtype=torch.float32, device=qkv.device)
             part_ml = torch.empty((step.n_seqs * n_heads * n_splits * 2,), dtype=torch.float32, device=qkv.device)
+        if kind == "tensor cores":
+            lib = _bind()
+            _cuda(qkv, "queries")
+            if qkv.dtype != torch.bfloat16 or memory.k.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+                raise KernelError("the tensor-core decode attention takes bfloat16 queries, cache and output")
+            _check(lib, lib.gi_attn_decode_kr_ex(
+                out.data_ptr(), _rows(out, "attention output"), part_o.data_ptr() if part_o is not None else None,
+                part_ml.data_ptr() if part_ml is not None else None, qkv.data_ptr(), _rows(qkv, "queries"), memory.k.data_ptr(),
+                memory.v.data_ptr(), _i32(memory.block_table, "block table"), memory.block_table.shape[1],
+                _i32(step.seq_slots, "slots"), _i32(step.seq_lens, "lengths"), step.n_seqs, n_heads, n_kv, head_dim, float(scale),
+                int(window or 0), int(n_splits), int(own_tiles), v_dim, float(softcap or 0.0), _sinks_ptr(sinks, n_heads),
+                int(chunk or 0), _stream()), 2 if n_splits > 1 else 1)
+            return out
         return attn_decode_generic(qkv, memory.k, memory.v, memory.block_table, step.seq_slots, step.seq_lens, step.n_seqs,
                                    n_heads, n_kv, head_dim, scale, window, n_splits, out, part_o, part_ml, own_tiles=own_tiles,
                                    **opts)
@@ -1300,17 +1317,33 @@ def attn_prefill_tc_general(q: torch.Tensor, kcache: torch.Tensor, vcache: torch
     return out
 
 
+def attn_general_tc_ok(dtype: torch.dtype, head_dim: int, v_dim: int) -> bool:
+    """Whether `attention_general` has tensor-core kernels for these sizes: bfloat16, multiples of 8 up to 128."""
+    return bool(TUNE["attn_general_tc"] and dtype == torch.bfloat16 and head_dim % 8 == 0 and v_dim % 8 == 0
+                and 0 < head_dim <= 128 and 0 < v_dim <= 128)
+
+
 def attn_general_decode_plan(n_seqs: int, max_kv_len: int, sm_count: int, n_heads: int, n_kv: int, window: Optional[int],
-                             chunk: Optional[int], dtype: torch.dtype):
-    """(slices in the launch, tiles per slice) for one-token steps of `attention_general`: slices of eight 32-key tiles
-    counted from the start of the span a query can see (the last `window` positions, its chunk, or everything), so
-    that a sequence's sums are formed in the same order whatever else the step holds."""
+                             chunk: Optional[int], dtype: torch.dtype, head_dim: Optional[int] = None,
+                             v_dim: Optional[int] = None, kv_lens=None):
+    """(kernel, slices in the launch, tiles per slice) for one-token steps of `attention_general`.
+    "tensor cores" (bfloat16, sizes the kernel takes): the cut `attn_decode_plan` makes for the keys-on-rows kernel, over
+    the span a token can see.  "plain": slices of eight 32-key tiles counted from the start of that span (the last
+    `window` positions, the token's chunk, or everything), so that a sequence's sums are formed in the same order
+    whatever else the step holds."""
+    limit = window or chunk
+    if head_dim is not None and attn_general_tc_ok(dtype, head_dim, v_dim or head_dim):
+        seen = min(max_kv_len, int(limit) + 15) if limit else max_kv_len
+        lens = [min(int(n), seen) for n in kv_lens] if kv_lens else None
+        n_splits, own = attn_decode_plan(n_seqs, seen, sm_count, n_heads, n_kv, 64 if max(head_dim, v_dim or head_dim) <= 64 else 128,
+                                         limit, torch.bfloat16, lens)
+        return "tensor cores", n_splits, own
     span = max_kv_len
     for limit in (window, chunk):
         if limit:
             span = min(span, int(limit) + 31)
     tiles = (span + 31) // 32 + (1 if (window or chunk) else 0)
-    return max(1, (tiles + OWN_LENGTH_TILES - 1) // OWN_LENGTH_TILES), OWN_LENGTH_TILES
+    return "plain", max(1, (tiles + OWN_LENGTH_TILES - 1) // OWN_LENGTH_TILES), OWN_LENGTH_TILES
 
 
 def act_mul(gate_up: torch.Tensor, act: str, out: Optional[torch.Tensor] = None, interleaved: bool = False) -> torch.Tensor:
@@ -1441,10 +1474,21 @@ def moe_plan(ids: torch.Tensor, experts: int):
     return offsets, perm, inv
 
 
+def moe_gather_rows(h: torch.Tensor, perm: torch.Tensor, top: int) -> torch.Tensor:
+    """The step's rows in the order of the sort by expert: out[r] = h[perm[r] // top]."""
+    lib = _bind()
+    _cuda(h, "activations")
+    out = torch.empty((perm.numel(), h.shape[1]), dtype=h.dtype, device=h.device)
+    _check(lib, lib.gi_moe_gather_rows(out.data_ptr(), h.data_ptr(), _dt(h, "activations"), _rows(h, "activations"),
+                                       _i32(perm, "permutation"), perm.numel(), int(top), h.shape[1], _stream()))
+    return out
+
+
 def moe_experts(h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, offsets: torch.Tensor, perm: torch.Tensor,
-                top: int) -> torch.Tensor:
+                top: int, interleaved: bool = False) -> torch.Tensor:
     """Every chosen expert's output, float32 [entries (in sorted order), width]: down_e(silu(gate_e h) * (up_e h)).
-    `w_gate_up` [experts, 2 f, width] (gate rows, then up rows), `w_down` [experts, width, f]."""
+    `w_gate_up` [experts, 2 f, width] (gate rows, then up rows; or, `interleaved`, blocks [8 gate | 8 up]), `w_down`
+    [experts, width, f].  Few entries (one-token steps) take kernels that stream the chosen experts' matrices once."""
     lib = _bind()
     _cuda(h, "activations")
     lda = _rows(h, "activations")
@@ -1458,7 +1502,8 @@ def moe_experts(h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, 
     inter = torch.empty((entries, f), dtype=h.dtype, device=h.device)
     _check(lib, lib.gi_moe_gemm_gate_up(inter.data_ptr(), _dt(h, "activations"), h.data_ptr(), lda, w_gate_up.data_ptr(),
                                         _dt(w_gate_up, "expert weights"), w_gate_up.stride(0), _i32(offsets, "offsets"),
-                                        _i32(perm, "permutation"), entries, int(top), experts, f, width, _stream()))
+                                        _i32(perm, "permutation"), entries, int(top), experts, f, width, int(interleaved),
+                                        _stream()))
     down = torch.empty((entries, width), dtype=torch.float32, device=h.device)
     _check(lib, lib.gi_moe_gemm_down(down.data_ptr(), inter.data_ptr(), _dt(inter, "activations"), f, w_down.data_ptr(),
                                      _dt(w_down, "expert weights"), w_down.stride(0), _i32(offsets, "offsets"), entries,

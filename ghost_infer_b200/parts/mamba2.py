@@ -82,11 +82,13 @@ class Mamba2(Mixer):
             raise RuntimeError("the state-space mixer was given no per-sequence state")
         with ops.bucket("qkv matmul"):
             proj = linear(h, self.w_in, out_dtype=self.rt.dtype)
-        with ops.bucket("attention"):
+        with ops.bucket("conv"):
             xbc = ops.mamba2_conv(proj, self.conv_w, self.conv_b, memory.state, step, self.inner, self.channels, self.taps,
                                   self.s_floats)
+        with ops.bucket("scan"):
             y = ops.mamba2_scan(xbc, proj, self.dt_bias, self.a_log, self.d_skip, memory.state, step, self.heads,
                                 self.head_dim, self.n_state, self.groups, self.taps)
+        with ops.bucket("gated norm"):
             g = ops.mamba2_gate_norm(y, proj, self.norm_w, self.norm_groups, self.eps, self.rt.dtype)
         with ops.bucket("out matmul"):
             linear(g, self.w_o, out=residual, accumulate=True)

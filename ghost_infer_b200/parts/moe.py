@@ -6,7 +6,9 @@ weighted sum.  A shared expert of the same form (if the model has one) runs for 
 by sigmoid(w_sg . h), one number per token.  residual += all of it.
 
 On the device the (token, choice) entries are sorted by expert without the host learning the counts, so a step's
-launches do not depend on what the router chose and one-token steps can be recorded and replayed.
+launches do not depend on what the router chose and one-token steps can be recorded and replayed.  A prompt step in
+bfloat16 with enough rows per expert reads the counts back (one wait per layer) and runs each expert's rows through
+the tensor-core products the dense feed-forward uses, its gate and up rows interleaved for their gated epilogue.
 
 Tensor names: prefix + "mlp.router", "mlp.e<i>.{gate,up,down}", "mlp.shared.{gate,up,down,sg}" unless
 `params["tensor_names"]` replaces the stems "router", "expert" (a format with `{i}`) or "shared".
@@ -55,11 +57,22 @@ class RoutedExperts(FeedForward):
     def bind(self, tensors, rt) -> None:
         super().bind(tensors, rt)
         self.w_router = rt.place(tensors[self.router_name])
-        gate_up = [torch.cat([tensors[self._expert(i, "gate")], tensors[self._expert(i, "up")]], dim=0) for i in range(self.experts)]
-        self.w_gate_up = rt.place(torch.stack(gate_up))                                   # [E, 2 f, d]: gate rows, then up rows
+        # [E, 2 f, d]: gate rows, then up rows; on the 16-bit path in blocks [8 gate | 8 up], as the products' gated
+        # epilogue wants them (the kernels here read either layout)
+        self.interleaved = rt.dtype == torch.bfloat16 and self.ff % 8 == 0 and rt.device.type == "cuda"
+        gate_up = []
+        for i in range(self.experts):
+            g, u = tensors[self._expert(i, "gate")], tensors[self._expert(i, "up")]
+            if self.interleaved:
+                gate_up.append(torch.stack([g.reshape(self.ff // 8, 8, self.hidden), u.reshape(self.ff // 8, 8, self.hidden)], dim=1)
+                               .reshape(2 * self.ff, self.hidden))
+            else:
+                gate_up.append(torch.cat([g, u], dim=0))
+        self.w_gate_up = rt.place(torch.stack(gate_up))
         self.w_down = rt.place(torch.stack([tensors[self._expert(i, "down")] for i in range(self.experts)]))   # [E, d, f]
         if self.w_gate_up.dtype != self.w_down.dtype:
             self.w_gate_up, self.w_down = self.w_gate_up.float(), self.w_down.float()
+        self.interleaved = self.interleaved and self.w_gate_up.dtype == torch.bfloat16
         self.w_sg = None
         if self.shared_ff:
             s = self.shared_stem
@@ -77,11 +90,36 @@ class RoutedExperts(FeedForward):
             self.w_shared_down = rt.place(tensors[s + "down"])
             self.w_sg = rt.place(tensors[s + "sg"]).reshape(-1).to(self.w_router.dtype).contiguous()
 
+    # rows per expert, on average, from which a prompt step takes the tensor-core products expert by expert
+    ROWS_FOR_TENSOR_CORES = 96
+
+    def _by_expert(self, h, step) -> bool:
+        return (self.interleaved and not step.is_decode and h.dtype == torch.bfloat16 and self.hidden % 8 == 0
+                and h.shape[0] * self.top >= self.ROWS_FOR_TENSOR_CORES * self.experts and not torch.cuda.is_current_stream_capturing())
+
+    def _experts_one_by_one(self, h, offsets, perm):
+        """The experts' outputs for a prompt step: the rows gathered in sorted order, then for every expert with rows
+        the gated product and the down product over its stretch.  The host waits for the counts here."""
+        rows = ops.moe_gather_rows(h, perm, self.top)
+        bounds = offsets.cpu().tolist()
+        down = torch.empty((rows.shape[0], self.hidden), dtype=torch.float32, device=h.device)
+        for e in range(self.experts):
+            lo, hi = bounds[e], bounds[e + 1]
+            if hi > lo:
+                act = ops.swiglu_interleaved(rows[lo:hi], self.w_gate_up[e])
+                linear(act, self.w_down[e], out=down[lo:hi])
+        return down
+
     def forward(self, h, residual, step) -> None:
-        with ops.bucket("ffn matmul"):
+        with ops.bucket("router"):
             ids, wts, sgate = ops.moe_route(h, self.w_router, self.top, self.w_sg)
             offsets, perm, inv = ops.moe_plan(ids, self.experts)
-            down = ops.moe_experts(h, self.w_gate_up, self.w_down, offsets, perm, self.top)
+        with ops.bucket("experts"):
+            if self._by_expert(h, step):
+                down = self._experts_one_by_one(h, offsets, perm)
+            else:
+                down = ops.moe_experts(h, self.w_gate_up, self.w_down, offsets, perm, self.top, self.interleaved)
+        with ops.bucket("ffn matmul"):
             shared = None
             if self.shared_ff:
                 if self.shared_interleaved:

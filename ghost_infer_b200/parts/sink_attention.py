@@ -71,7 +71,7 @@ class SinkAttention(Mixer):
 
     def decode_plan(self, n_seqs: int, max_kv_len: int, sm_count: int, kv_lens=None):
         return ops.attn_general_decode_plan(n_seqs, max_kv_len, sm_count, self.n_heads, self.n_kv, self.window, self.chunk,
-                                            self.rt.dtype)
+                                            self.rt.dtype, self.head_dim, self.v_dim, kv_lens)
 
     def bind(self, tensors, rt) -> None:
         super().bind(tensors, rt)
