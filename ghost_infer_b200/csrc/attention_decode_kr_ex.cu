@@ -3,7 +3,7 @@
 // gi_attn_combine) with what some designs add to attention, each off at its neutral value:
 //  * keys and values of different widths (hd, hdv: any multiples of 8 up to 128; tiles are padded with zero columns to
 //    64 or 128, which add nothing to a product);
-//  * a cap on the scores, s <- cap * tanh(s / cap), in 32-bit with the accurate tanh;
+//  * a cap on the scores, s <- cap * tanh(s / cap), in 32-bit (tanh through the approximate exponential: see gi::tanh_fast);
 //  * a sink per head: one more term exp(sink) in the denominator, with no key and no value (the first slice takes it in);
 //  * chunks: the token sees the keys of its own chunk floor(pos / chunk) only, counted from position 0.
 #include <math.h>
@@ -166,7 +166,7 @@ attn_decode_krx_kernel(__nv_bfloat16* __restrict__ out, long ldo, float* __restr
     const bool ok0 = t0 + g < len && t0 + g >= t_first, ok1 = t0 + g + 8 < len && t0 + g + 8 >= t_first;
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
-      const float sc = softcap > 0.f ? cap_out * tanhf(s[c] * cap_in) : s[c] * sl2;
+      const float sc = softcap > 0.f ? cap_out * gi::tanh_fast(s[c] * cap_in) : s[c] * sl2;
       s[c] = ((c < 2) ? ok0 : ok1) ? sc : -INFINITY;
     }
     float alpha[2];

@@ -3,7 +3,7 @@
 // base 2 with 32-bit statistics) with what some designs add to attention, each off at its neutral value:
 //  * keys and values of different widths (hd, hdv: any multiples of 8 up to 128; tiles are padded with zero columns to
 //    64 or 128, which add nothing to a product);
-//  * a cap on the scores, s <- cap * tanh(s / cap), in 32-bit with the accurate tanh;
+//  * a cap on the scores, s <- cap * tanh(s / cap), in 32-bit (tanh through the approximate exponential: see gi::tanh_fast);
 //  * a sink per head: one more term exp(sink) in the denominator, with no key and no value;
 //  * chunks: a query sees the keys of its own chunk floor(pos / chunk) only, counted from position 0.
 #include <math.h>
@@ -144,7 +144,7 @@ attn_prefill_tcx_kernel(__nv_bfloat16* __restrict__ out, long ldo, const __nv_bf
           const int key = kt + nt * 8 + 2 * t + (c & 1);
           const int p = p_row0 + (c >> 1) * 8;
           const bool ok = key <= p && p <= p_last && (window <= 0 || key > p - window) && key >= c_lo[c >> 1];
-          const float sc = softcap > 0.f ? cap_out * tanhf(s[nt][c] * cap_in) : s[nt][c] * sl2;
+          const float sc = softcap > 0.f ? cap_out * gi::tanh_fast(s[nt][c] * cap_in) : s[nt][c] * sl2;
           s[nt][c] = ok ? sc : -INFINITY;
           tmax[c >> 1] = fmaxf(tmax[c >> 1], s[nt][c]);
         }

@@ -81,6 +81,15 @@ __device__ __forceinline__ float gated_mul_bf16(float g, float u, int act) {
   return act ? gelu_tanh_mul_bf16(g, u) : silu_mul_bf16(g, u);
 }
 
+// tanh for the capped scores of the 16-bit attention kernels: 1 - 2 / (e^(2x) + 1) with the approximate exponential and
+// division (absolute error about 1e-7, far below what the rounding of queries and keys to 8 bits leaves in a score; the
+// ends are right: +1 for large x, -1 for large -x).  The 32-bit path uses tanhf.
+__device__ __forceinline__ float tanh_fast(float x) {
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * 2.8853900817779268f));
+  return 1.0f - __fdividef(2.0f, e + 1.0f);
+}
+
 // Four neighbouring values at once (the pointer is aligned to the four of them).
 __device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
 __device__ __forceinline__ float4 ld4(const __nv_bfloat16* p) {

@@ -6,10 +6,12 @@
 //  * scan:  dt <- softplus(dt + dt_bias); per head (head h reads group h / (heads / G) of B and C)
 //           S <- exp(-exp(A_log) dt) S + dt B x^T   (S is N x P),   y = S^T C + D x.
 //           Everything here is 32-bit; the tokens of a sequence are walked in order, thirty-two at a time through shared
-//           memory; a warp owns four columns p of S, its lanes the rows n, kept in registers across the step.
+//           memory; a warp owns two or four columns p of S, its lanes the rows n, kept in registers across the step.
 //           One token or a thousand, alone or in a batch, take the same arithmetic in the same order: no bit changes.
 //  * gate + norm: y * silu(z), divided by the root mean square of each of `parts` equal parts, times a weight.
-// Per-sequence state: one float row per slot, [S: heads * N * P | last taps - 1 conv inputs: (taps - 1) * channels];
+// Per-sequence state: one float row per slot, [S: heads * P * N, a column's N rows side by side (a lane's rows are then
+// neighbours in memory: a one-token step, which is all loading and storing of S, moves whole lines) | last taps - 1 conv
+// inputs: (taps - 1) * channels];
 // slot -1 (a padding row of a fixed-size launch) uses the last row of the matrix.
 #include <math.h>
 
@@ -77,14 +79,14 @@ __global__ void conv_update_kernel(const T* __restrict__ proj, long ld_proj, flo
   }
 }
 
-// grid (heads, sequences, column tiles of SC_W * SC_CPW); a warp owns SC_CPW columns p of the head's state, its lanes the
+// grid (heads, sequences, column tiles of SC_W * SC_CPW); a warp owns SC_CPW (two or four) columns p of the head's state, its lanes the
 // rows (lane l of NPT >= 4 rows owns rows (32 j + l) 4 .. + 3 for j = 0 .. NPT / 4 - 1, so that a warp reads B and C as
 // whole 16-byte words side by side; of fewer rows, l NPT .. + NPT - 1), in registers for the whole step.  Tokens go
 // through shared memory SC_CH at a time (rows past N padded with zeros, which leave their state at zero); B_t and C_t
 // are read once per token for all of a warp's columns.  A token's sum over the rows stays per lane for SC_RB tokens,
 // then the 32 (token, column) sums of a warp are added across its lanes in one halving exchange (31 shuffles instead of
-// 160), after which lane 4 t + c holds token t, column c.  The order of every sum follows from N alone.
-constexpr int SC_W = 4, SC_CPW = 4, SC_COLS = SC_W * SC_CPW, SC_CH = 32, SC_RB = 8;
+// 160), after which lane SC_CPW t + c holds token t, column c.  The order of every sum follows from N alone.
+constexpr int SC_W = 4, SC_CH = 32;
 
 // One halving step of the exchange: of 2 * HALF values a lane keeps the half its bit `BIT` of the lane number names and
 // adds the other lane's partial sums of the same values.
@@ -99,13 +101,15 @@ __device__ __forceinline__ void halve(float (&v)[32], int lane) {
   }
 }
 
-template <typename T, typename TW, int NPT>
+template <typename T, typename TW, int NPT, int SC_CPW>
 __global__ void __launch_bounds__(SC_W * 32)
 scan_kernel(float* __restrict__ y, const T* __restrict__ xbc, const T* __restrict__ proj, long ld_proj,
             const TW* __restrict__ dt_bias, const TW* __restrict__ a_log, const TW* __restrict__ d_skip,
             float* __restrict__ state, long state_ld, int state_rows, const int* __restrict__ cu_seqlens,
             const int* __restrict__ seq_slots, int heads, int P, int N, int groups) {
   constexpr int NP = 32 * NPT;       // rows with padding
+  constexpr int SC_COLS = SC_W * SC_CPW, SC_RB = 32 / SC_CPW, SC_CPW_LOG2 = SC_CPW == 2 ? 1 : 2;
+  static_assert(SC_CPW == 2 || SC_CPW == 4, "a warp takes 2 or 4 columns");
   extern __shared__ __align__(16) float sm[];
   float* sB = sm;                    // [SC_CH][NP]
   float* sC = sB + SC_CH * NP;       // [SC_CH][NP]
@@ -130,7 +134,7 @@ scan_kernel(float* __restrict__ y, const T* __restrict__ xbc, const T* __restric
 #pragma unroll
     for (int i = 0; i < NPT; ++i) {
       const int n = row_of(i);
-      S[c][i] = (pw + c < P && n < N) ? S_row[(size_t)n * P + pw + c] : 0.f;
+      S[c][i] = (pw + c < P && n < N) ? S_row[(size_t)(pw + c) * N + n] : 0.f;
     }
   const float A = -expf(gi::ldf(a_log + h)), D = gi::ldf(d_skip + h), bias = gi::ldf(dt_bias + h);
 
@@ -203,8 +207,8 @@ scan_kernel(float* __restrict__ y, const T* __restrict__ xbc, const T* __restric
       halve<4, 4>(acc, lane);
       halve<2, 2>(acc, lane);
       halve<1, 1>(acc, lane);
-      // lane 4 tl + c now holds token t0 + tl, column c
-      const int t = t0 + (lane >> 2), c = lane & 3;
+      // lane SC_CPW tl + c now holds token t0 + tl, column c
+      const int t = t0 + (lane >> SC_CPW_LOG2), c = lane & (SC_CPW - 1);
       if (t < nc && pw + c < P)
         y[(size_t)(tok0 + c0 + t) * inner + (size_t)h * P + pw + c] = acc[0] + D * sx[t * SC_COLS + warp * SC_CPW + c];
     }
@@ -214,7 +218,7 @@ scan_kernel(float* __restrict__ y, const T* __restrict__ xbc, const T* __restric
 #pragma unroll
     for (int i = 0; i < NPT; ++i) {
       const int n = row_of(i);
-      if (pw + c < P && n < N) S_row[(size_t)n * P + pw + c] = S[c][i];
+      if (pw + c < P && n < N) S_row[(size_t)(pw + c) * N + n] = S[c][i];
     }
 }
 
@@ -239,11 +243,11 @@ gate_norm_kernel(TO* __restrict__ out, const float* __restrict__ y, const T* __r
   }
 }
 
-template <typename T, typename TW, int NPT>
+template <typename T, typename TW, int NPT, int CPW>
 int launch_scan(dim3 grid, size_t smem, cudaStream_t s, float* y, const T* xbc, const T* proj, long ld_proj, const TW* dt_bias,
                 const TW* a_log, const TW* d_skip, float* state, long state_ld, int state_rows, const int* cu, const int* slots,
                 int heads, int P, int N, int groups) {
-  auto kern = scan_kernel<T, TW, NPT>;
+  auto kern = scan_kernel<T, TW, NPT, CPW>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return gi::fail(GI_ERR_CUDA, "mamba2 scan: %s", cudaGetErrorString(e));
@@ -295,17 +299,25 @@ extern "C" int gi_mamba2_scan(float* y, const void* xbc, const void* proj, int d
   if (N > 1024) return gi::fail(GI_ERR_UNSUPPORTED, "mamba2 scan: a state of %d rows is more than a warp's lanes take", N);
   int npt = 1;
   while (32 * npt < N) npt *= 2;
-  dim3 grid(heads, n_seqs, (P + SC_COLS - 1) / SC_COLS);
+  // four columns a warp where that still gives every SM several blocks (B_t and C_t are then read once for four columns);
+  // two where there are few heads and sequences (one prompt), for twice the warps.  Either way a sum's additions are
+  // the same ones in the same order, so the choice changes no bit.
+  const int cpw = ((long)heads * n_seqs * ((P + SC_W * 4 - 1) / (SC_W * 4)) >= 400) ? 4 : 2;
+  const int cols = SC_W * cpw;
+  dim3 grid(heads, n_seqs, (P + cols - 1) / cols);
   if (grid.z > 65535) return gi::fail(GI_ERR_UNSUPPORTED, "mamba2 scan: head size %d is more than one launch takes", P);
-  const size_t smem = (2 * (size_t)SC_CH * 32 * npt + (size_t)SC_CH * SC_COLS + 2 * SC_CH) * sizeof(float);
+  const size_t smem = (2 * (size_t)SC_CH * 32 * npt + (size_t)SC_CH * cols + 2 * SC_CH) * sizeof(float);
   cudaStream_t s = (cudaStream_t)stream;
   int rc = GI_OK;
+#define GI_SCAN_LAUNCH(NPT, CPW)                                                                                       \
+  GI_DISPATCH_DTYPE(dtype, T, GI_DISPATCH_DTYPE(w_dtype, TW,                                                           \
+      rc = (launch_scan<T, TW, NPT, CPW>(grid, smem, s, y, (const T*)xbc, (const T*)proj, ld_proj, (const TW*)dt_bias, \
+                                         (const TW*)a_log, (const TW*)d_skip, state, state_ld, state_rows, cu_seqlens, \
+                                         seq_slots, heads, P, N, groups))))
 #define GI_SCAN_CASE(NPT)                                                                                              \
   case NPT:                                                                                                            \
-    GI_DISPATCH_DTYPE(dtype, T, GI_DISPATCH_DTYPE(w_dtype, TW,                                                         \
-        rc = (launch_scan<T, TW, NPT>(grid, smem, s, y, (const T*)xbc, (const T*)proj, ld_proj, (const TW*)dt_bias,    \
-                                      (const TW*)a_log, (const TW*)d_skip, state, state_ld, state_rows, cu_seqlens,    \
-                                      seq_slots, heads, P, N, groups))));                                              \
+    if (cpw == 4) GI_SCAN_LAUNCH(NPT, 4);                                                                              \
+    else GI_SCAN_LAUNCH(NPT, 2);                                                                                       \
     break;
   switch (npt) {
     GI_SCAN_CASE(1)
@@ -315,6 +327,7 @@ extern "C" int gi_mamba2_scan(float* y, const void* xbc, const void* proj, int d
     GI_SCAN_CASE(16)
     GI_SCAN_CASE(32)
   }
+#undef GI_SCAN_LAUNCH
 #undef GI_SCAN_CASE
   return rc;
 }

@@ -389,7 +389,7 @@ combine_kernel(float* __restrict__ residual, const float* __restrict__ down, con
                int top) {
   gi::pdl_prologue();
   const int t = blockIdx.x;
-  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < width; i += gridDim.y * blockDim.x) {
     float acc = 0.f;
     for (int k = 0; k < top; ++k)
       acc = fmaf(wts[(size_t)t * top + k], down[(size_t)inv[(size_t)t * top + k] * width + i], acc);
@@ -500,7 +500,9 @@ extern "C" int gi_moe_combine(float* residual, const float* down, const int* inv
                               const float* sgate, int n_tokens, int width, int top, void* stream) {
   if (n_tokens <= 0) return GI_OK;
   if (shared != nullptr && sgate == nullptr) return gi::fail(GI_ERR_ARG, "expert combine: a shared output needs its gate");
-  return gi::check(gi::launch(combine_kernel, dim3(n_tokens), dim3(256), 0, (cudaStream_t)stream, residual, down, inv, wts, shared,
+  // few tokens: a row's columns over several blocks
+  const int col_blocks = n_tokens >= 256 ? 1 : min(64, (width + 255) / 256);
+  return gi::check(gi::launch(combine_kernel, dim3(n_tokens, col_blocks), dim3(256), 0, (cudaStream_t)stream, residual, down, inv, wts, shared,
                               sgate, width, top), "expert combine");
 }
 
