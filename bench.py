@@ -114,7 +114,7 @@ def measure_workload(key, new_tokens=None, clocks=None, no_pdl=False):
 def _barovik(width, heads, kv, dim, vdim, chunk, ff, ssm_heads, ssm_dim, state, groups, experts, top, expert_ff, shared_ff,
              vocab, pairs):
     att = {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": vdim, "scale": dim ** -0.5,
-                                          "softcap": 50.0, "mask": {"size": chunk}, "v_mix": True},
+                                          "softcap": 30.0, "mask": {"size": chunk}, "v_mix": True},
            "mlp": {"kind": "dense", "ff": ff}}
     ssm = {"type": "mamba2", "mixer": {"heads": ssm_heads, "vdim": ssm_dim, "state": state, "groups": groups, "conv": 4,
                                        "norm_groups": groups},
@@ -136,7 +136,7 @@ HYBRID_SIZES = {
                   experts=16, top=2, expert_ff=2048, shared_ff=2048, vocab=32000, pairs=2),
     "w4096": dict(width=4096, heads=32, kv=8, dim=128, vdim=128, chunk=8192, ff=14336, ssm_heads=128, ssm_dim=64, state=128, groups=8,
                   experts=16, top=2, expert_ff=4096, shared_ff=4096, vocab=32000, pairs=2),
-    "w2048_odd": dict(width=2048, heads=32, kv=8, dim=64, vdim=48, chunk=1000, ff=8192, ssm_heads=64, ssm_dim=48, state=96, groups=4,
+    "w2048_odd": dict(width=2048, heads=32, kv=8, dim=64, vdim=40, chunk=1000, ff=8192, ssm_heads=64, ssm_dim=40, state=96, groups=4,
                       experts=32, top=4, expert_ff=1024, shared_ff=2048, vocab=32000, pairs=2),
 }
 

@@ -428,3 +428,67 @@ def test_greedy_generation_through_the_entry_point(tmp_path):
         want = seq[len(p):]
         assert r.tokens[:len(want)] == want, f"prompt of {len(p)}: {r.tokens} vs {want}"
     assert llm.cache.free_pages == llm.cache.n_pages
+
+
+# ---- configurations drawn at random ------------------------------------------------------------------------------------
+def random_config(seed, all_experts):
+    """Sizes drawn from lists that mix multiples of 8 with numbers that are not (which take the kernels' plain paths)."""
+    r = np.random.default_rng(seed)
+    pick = lambda xs: int(xs[r.integers(len(xs))])
+    width = pick([40, 56, 72, 100, 132])
+    kv, vdim_att = pick([1, 2, 3]), pick([8, 12, 24, 40])
+    shared_attention = attn(kv * pick([1, 2, 4]), kv, pick([8, 20, 32, 48]), vdim_att, pick([5, 17, 64, 90]),
+                            float(r.uniform(0.1, 0.5)), cap=pick([0, 7, 40]) or None, v_mix=True)
+    layers = []
+    for _ in range(pick([2, 3, 4])):
+        if r.random() < 0.5:
+            mixer = ("attention", shared_attention if r.random() < 0.7 else
+                     attn(pick([2, 4]), pick([1, 2]), pick([16, 24]), pick([16, 10]), pick([9, 33]), 0.3, v_mix=False))
+        else:
+            groups = pick([1, 2])
+            mixer = ("mamba2", ssm(groups * pick([1, 2, 3]), pick([4, 10, 16, 36]), pick([3, 16, 40, 130]), groups, pick([1, 2, 4, 5]), 1))
+            if (mixer[1]["heads"] * mixer[1]["vdim"]) % 2 == 0 and r.random() < 0.5:
+                mixer[1]["norm_groups"] = 2
+        kind = pick([0, 1, 2])
+        if kind == 0:
+            mlp = None
+        elif kind == 1:
+            mlp = dense(pick([24, 52, 64]))
+        else:
+            experts = pick([2, 5, 9])
+            mlp = moe(experts, experts if all_experts else pick([1, 2]), pick([8, 12, 40]), shared=pick([0, 16, 20]) or None)
+        layers.append(layer(mixer[0], mixer[1], mlp))
+    return model_cfg(width, pick([50, 97, 260]), layers, scale=float(r.uniform(0.5, 2.0)), eps=float(10 ** r.uniform(-6, -4)))
+
+
+@pytest.mark.parametrize("seed,dtype", [(s, "float32") for s in range(6)] + [(s, "bfloat16") for s in range(100, 104)])
+def test_configurations_drawn_at_random(seed, dtype):
+    """Whole prompt, prompt cut in three, the tail token by token, and a batch of three, on a model nobody chose."""
+    cfg = random_config(seed, all_experts=dtype == "bfloat16")
+    w = pb.random_weights(cfg, seed=seed)
+    tensors = {k: torch.from_numpy(np.asarray(v, dtype=np.float32)).to(torch.bfloat16) for k, v in w.items()}
+    model = gi.Model.from_config_dict(cfg).bind(tensors, dtype, "cuda:0")
+    eng = gi.Engine(model, model.new_cache(max_tokens=64 * 24, max_seq_len=1024))
+    r = np.random.default_rng(seed + 1)
+    prompts = [r.integers(0, cfg["vocab"], size=n).tolist() for n in (150, 70, 9)]
+    refs = [pb.forward(cfg, w, p) for p in prompts]
+    check(run_whole(eng, prompts[0]), refs[0], dtype, f"{cfg}: whole")
+    s = eng.cache.open_slot()
+    rows = [eng.step([gi.StepEntry(s, prompts[0][a:b], list(range(b - a)))]).cpu().numpy() for a, b in ((0, 2), (2, 67), (67, 130))]
+    run = eng.decoder([s])
+    rows += [run.forward(tokens=[t]).cpu().numpy().copy() for t in prompts[0][130:]]
+    eng.cache.close_slot(s)
+    check(np.concatenate(rows, 0), refs[0], dtype, f"{cfg}: cut and decoded")
+    slots = [eng.cache.open_slot() for _ in prompts]
+    cut = [len(p) - 5 for p in prompts]
+    out = eng.step([gi.StepEntry(sl, p[:c], list(range(c))) for sl, p, c in zip(slots, prompts, cut)]).cpu().numpy()
+    got = [[out[sum(cut[:i]):sum(cut[:i + 1])]] for i in range(3)]
+    run = eng.decoder(slots)
+    for k in range(5):
+        step_rows = run.forward(tokens=[p[c + k] for p, c in zip(prompts, cut)]).cpu().numpy()
+        for i in range(3):
+            got[i].append(step_rows[i:i + 1].copy())
+    for sl in slots:
+        eng.cache.close_slot(sl)
+    for i in range(3):
+        check(np.concatenate(got[i], 0), refs[i], dtype, f"{cfg}: request {i} of a batch")

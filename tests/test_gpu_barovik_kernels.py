@@ -80,7 +80,7 @@ def attention_reference(q, k, v, pos0, q_lens, scale, cap, sinks, chunk, window)
 
 CASES = [
     # H, G, dk, dv, cap, sinks, chunk, window
-    (4, 2, 64, 48, 30.0, True, 100, None),
+    (4, 2, 64, 56, 30.0, True, 100, None),
     (6, 2, 40, 72, None, True, None, 70),
     (3, 3, 128, 128, 5.0, False, 33, None),
     (8, 1, 24, 8, None, False, None, None),
