@@ -492,3 +492,38 @@ def test_configurations_drawn_at_random(seed, dtype):
         eng.cache.close_slot(sl)
     for i in range(3):
         check(np.concatenate(got[i], 0), refs[i], dtype, f"{cfg}: request {i} of a batch")
+
+
+# ---- the replay program as a user runs it ----------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_replay_program(tmp_path, dtype):
+    """`bin/trace_run` on a model folder: requests whole, tails token by token, and unequal batches decoded together."""
+    import subprocess
+    import sys
+    from test_gpu_trace_run import build_trace
+    cfg, w, _ = made("B")
+    d = tmp_path / "model"
+    d.mkdir()
+    (d / "config.json").write_text(json.dumps(cfg))
+    pb.write_safetensors_bf16(str(d / "model.safetensors"), w)
+    reqs, steps = build_trace({"vocab_size": cfg["vocab"]})
+    out = tmp_path / "out"
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    p = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", str(d), "--dtype", dtype, "--out", str(out),
+                        "--max-tokens", str(64 * 8)], input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True,
+                       text=True, timeout=900)
+    assert p.returncode == 0, p.stderr[-3000:]
+    assert p.stdout.split("\n")[:len(steps)] == [f"done {i}" for i in range(len(steps))]
+    refs = {rid: pb.forward(cfg, w, toks) for rid, toks in reqs.items()}
+    place = {}
+    for s in steps:
+        want_rows = []
+        for e in s["entries"]:
+            base = place.get(e["id"], 0)
+            want_rows += [refs[e["id"][:2]][base + k] for k in e["want"]]
+            place[e["id"]] = base + len(e["tokens"])
+        f = out / f"{s['step']}.f32"
+        if want_rows:
+            check(np.fromfile(f, dtype="<f4").reshape(-1, cfg["vocab"]), np.stack(want_rows), dtype, f"step {s['step']}")
+        else:
+            assert not f.exists()
