@@ -270,6 +270,11 @@ int gi_moe_gather_rows(void* out, const void* in, int dtype, long ld_in, const i
                        void* stream);
 int gi_moe_gemm_down(float* out, const void* a, int dtype, long lda, const void* w, int w_dtype, long w_stride,
                      const int* offsets, int entries, int experts, int n, int k, void* stream);
+// The experts of a prompt step through the tcgen05 products, one expert's stretch of the sorted rows after another, from
+// offsets on the HOST (int[experts + 1]); bfloat16, gate and up rows interleaved.  hidden: bfloat16 [entries, f] scratch.
+int gi_moe_experts_tc(float* out, void* hidden, const void* rows, const void* w_gate_up, long gate_up_stride,
+                      const void* w_down, long down_stride, const int* host_offsets, int experts, int width, int f,
+                      float* scratch, int* counters, int n_counters, void* stream);
 // residual[t, :] += sum_k wts[t, k] * down[inv[t * top + k], :] (k in order) + sgate[t] * shared[t, :] (if given).
 int gi_moe_combine(float* residual, const float* down, const int* inv, const float* wts, const float* shared,
                    const float* sgate, int n_tokens, int width, int top, void* stream);

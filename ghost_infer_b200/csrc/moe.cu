@@ -515,3 +515,36 @@ extern "C" int gi_moe_gather_rows(void* out, const void* in, int dtype, long ld_
                                              (const T*)in, ld_in, perm, top, width));
   return gi::check(e, "gather rows");
 }
+
+// A prompt step's experts through the tensor-core products, expert by expert, from offsets the host has read back: for
+// every expert with rows, hidden = act(rows W_gate^T) * (rows W_up^T) (gate and up rows interleaved in blocks of 8) and
+// out = hidden W_down^T as float, over the expert's stretch of the sorted rows.  Stretches of up to 64 rows take the
+// streamed product, longer ones the tiled one.  One call per layer, so that the host's share is the launches alone.
+extern "C" int gi_moe_experts_tc(float* out, void* hidden, const void* rows, const void* w_gate_up, long gate_up_stride,
+                                 const void* w_down, long down_stride, const int* host_offsets, int experts, int width, int f,
+                                 float* scratch, int* counters, int n_counters, void* stream) {
+  if (experts <= 0 || width <= 0 || f <= 0 || f % 8 != 0 || width % 8 != 0)
+    return gi::fail(GI_ERR_UNSUPPORTED, "experts on tensor cores: width %d and hidden width %d must be multiples of 8", width, f);
+  const __nv_bfloat16* a = (const __nv_bfloat16*)rows;
+  __nv_bfloat16* h = (__nv_bfloat16*)hidden;
+  for (int e = 0; e < experts; ++e) {
+    const int lo = host_offsets[e], m = host_offsets[e + 1] - lo;
+    if (m <= 0) continue;
+    const __nv_bfloat16* wgu = (const __nv_bfloat16*)w_gate_up + (size_t)e * gate_up_stride;
+    const __nv_bfloat16* wd = (const __nv_bfloat16*)w_down + (size_t)e * down_stride;
+    int rc;
+    if (m <= 64) {
+      rc = gi_gemm_stream_bf16(h + (size_t)lo * f, GI_SKINNY_SWIGLU, a + (size_t)lo * width, wgu, scratch, counters, n_counters, m,
+                               2 * f, width, width, width, f, -1, stream);
+      if (rc == GI_OK)
+        rc = gi_gemm_stream_bf16(out + (size_t)lo * width, GI_SKINNY_STORE_F32, h + (size_t)lo * f, wd, scratch, counters, n_counters,
+                                 m, width, f, f, f, width, -1, stream);
+    } else {
+      rc = gi_gemm_tc_bf16(h + (size_t)lo * f, GI_TC_SWIGLU, a + (size_t)lo * width, wgu, m, 2 * f, width, width, width, f, 256, stream);
+      if (rc == GI_OK)
+        rc = gi_gemm_tc_bf16(out + (size_t)lo * width, GI_TC_STORE_F32, h + (size_t)lo * f, wd, m, width, f, f, f, width, 256, stream);
+    }
+    if (rc != GI_OK) return rc;
+  }
+  return GI_OK;
+}

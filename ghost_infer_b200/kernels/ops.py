@@ -83,6 +83,7 @@ def _bind():
         "gi_moe_plan": [P, P, P, P, P, I, I, P],
         "gi_moe_gemm_gate_up": [P, I, P, L, P, I, L, P, P, I, I, I, I, I, I, P],
         "gi_moe_gather_rows": [P, P, I, L, P, I, I, I, P],
+        "gi_moe_experts_tc": [P, P, P, P, L, P, L, P, I, I, I, P, P, I, P],
         "gi_moe_gemm_down": [P, P, I, L, P, I, L, P, I, I, I, I, P],
         "gi_moe_combine": [P, P, P, P, P, P, I, I, I, P],
     }
@@ -1509,6 +1510,33 @@ def moe_experts(h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, 
                                      _dt(w_down, "expert weights"), w_down.stride(0), _i32(offsets, "offsets"), entries,
                                      experts, width, f, _stream()))
     return down
+
+
+def moe_experts_by_expert(rows: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, host_offsets) -> torch.Tensor:
+    """The experts' outputs, float32 [entries, width], for rows already in sorted order, through the tcgen05 products expert
+    by expert; `host_offsets`: the experts' offsets as Python integers (the caller has read them back).  bfloat16, gate and
+    up rows interleaved in blocks of 8."""
+    lib = _bind()
+    _cuda(rows, "sorted rows")
+    experts, f2, width = w_gate_up.shape
+    f = f2 // 2
+    entries = rows.shape[0]
+    if (rows.dtype != torch.bfloat16 or w_gate_up.dtype != torch.bfloat16 or w_down.dtype != torch.bfloat16 or not rows.is_contiguous()
+            or rows.shape[1] != width or tuple(w_down.shape) != (experts, width, f) or not w_gate_up.is_contiguous()
+            or not w_down.is_contiguous()):
+        raise KernelError("experts on tensor cores take contiguous bfloat16 rows and weights of fitting sizes")
+    if len(host_offsets) != experts + 1 or host_offsets[0] != 0 or host_offsets[-1] != entries or any(
+            b < a for a, b in zip(host_offsets, host_offsets[1:])):
+        raise KernelError("the experts' offsets do not cover the rows")
+    hidden = torch.empty((entries, f), dtype=torch.bfloat16, device=rows.device)
+    out = torch.empty((entries, width), dtype=torch.float32, device=rows.device)
+    scratch, counters = _stream_buffers(rows.device)
+    offs = (c_int * (experts + 1))(*[int(x) for x in host_offsets])
+    n_live = sum(1 for a, b in zip(host_offsets, host_offsets[1:]) if b > a)
+    _check(lib, lib.gi_moe_experts_tc(out.data_ptr(), hidden.data_ptr(), rows.data_ptr(), w_gate_up.data_ptr(), w_gate_up.stride(0),
+                                      w_down.data_ptr(), w_down.stride(0), offs, experts, width, f, scratch.data_ptr(),
+                                      counters.data_ptr(), counters.numel(), _stream()), 2 * n_live)
+    return out
 
 
 def moe_combine(residual: torch.Tensor, down: torch.Tensor, inv: torch.Tensor, wts: torch.Tensor,

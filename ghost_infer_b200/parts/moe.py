@@ -101,14 +101,7 @@ class RoutedExperts(FeedForward):
         """The experts' outputs for a prompt step: the rows gathered in sorted order, then for every expert with rows
         the gated product and the down product over its stretch.  The host waits for the counts here."""
         rows = ops.moe_gather_rows(h, perm, self.top)
-        bounds = offsets.cpu().tolist()
-        down = torch.empty((rows.shape[0], self.hidden), dtype=torch.float32, device=h.device)
-        for e in range(self.experts):
-            lo, hi = bounds[e], bounds[e + 1]
-            if hi > lo:
-                act = ops.swiglu_interleaved(rows[lo:hi], self.w_gate_up[e])
-                linear(act, self.w_down[e], out=down[lo:hi])
-        return down
+        return ops.moe_experts_by_expert(rows, self.w_gate_up, self.w_down, offsets.cpu().tolist())
 
     def forward(self, h, residual, step) -> None:
         with ops.bucket("router"):

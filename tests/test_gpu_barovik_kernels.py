@@ -274,3 +274,24 @@ def test_embedding_times_a_constant():
     tokens = torch.tensor([3, 49, 0, 3], dtype=torch.int32, device=DEV)
     assert torch.equal(ops.embed(table, tokens, scale=0.5), table[tokens.long()].float() * 0.5)
     assert torch.equal(ops.embed(table, tokens), table[tokens.long()].float())
+
+
+def test_experts_expert_by_expert_on_tensor_cores():
+    """A prompt step's way through the experts (rows gathered in sorted order, then each expert's stretch through the
+    tensor-core products) against the grouped kernel on the same rows; stretches of fewer and of more than 64 rows."""
+    g = torch.Generator().manual_seed(9)
+    T, E, top, d, f = 900, 7, 1, 72, 40
+    h = torch.randn(T, d, generator=g).to(torch.bfloat16).to(DEV)
+    wr = torch.randn(E, d, generator=g) * 0.4
+    wr[5] *= 0.05                                      # an expert that few tokens choose: a short stretch
+    gate, up = (torch.randn(E, f, d, generator=g) * 0.2).to(torch.bfloat16), (torch.randn(E, f, d, generator=g) * 0.2).to(torch.bfloat16)
+    gu = torch.stack([gate.reshape(E, f // 8, 8, d), up.reshape(E, f // 8, 8, d)], dim=2).reshape(E, 2 * f, d).contiguous().to(DEV)
+    down = (torch.randn(E, d, f, generator=g) * 0.2).to(torch.bfloat16).to(DEV)
+    ids, wts, _ = ops.moe_route(h, wr.to(torch.bfloat16).to(DEV), top)
+    offsets, perm, inv = ops.moe_plan(ids, E)
+    counts = np.diff(offsets.cpu().numpy())
+    assert counts.min() <= 64 < counts.max()
+    want = ops.moe_experts(h, gu, down, offsets, perm, top, True)
+    got = ops.moe_experts_by_expert(ops.moe_gather_rows(h, perm, top), gu, down, offsets.cpu().tolist())
+    ops.check_status()
+    assert (got - want).abs().max().item() < 0.02 * want.abs().max().item()
