@@ -527,23 +527,63 @@ extern "C" int gi_moe_experts_tc(float* out, void* hidden, const void* rows, con
     return gi::fail(GI_ERR_UNSUPPORTED, "experts on tensor cores: width %d and hidden width %d must be multiples of 8", width, f);
   const __nv_bfloat16* a = (const __nv_bfloat16*)rows;
   __nv_bfloat16* h = (__nv_bfloat16*)hidden;
+  cudaStream_t main_stream = (cudaStream_t)stream;
+  // An expert's stretch of a few hundred rows makes fewer tiles than the GPU has SMs, so the longer stretches go round
+  // four side streams (an expert's two products one after the other on its stream) between a fork and a join on the
+  // caller's stream; the short ones, whose streamed product shares its scratch memory, follow on the caller's stream.
+  constexpr int SIDE = 4;
+  static cudaStream_t side[gi::MAX_DEVICES_SEEN][SIDE];
+  static cudaEvent_t fork_ev[gi::MAX_DEVICES_SEEN], join_ev[gi::MAX_DEVICES_SEEN][SIDE];
+  static bool made[gi::MAX_DEVICES_SEEN] = {false};
+  int dev = -1;
+  bool many = false;
+  for (int e = 0; e < experts; ++e) many = many || host_offsets[e + 1] - host_offsets[e] > 64;
+  cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+  cudaStreamIsCapturing(main_stream, &capturing);
+  bool fan = many && capturing == cudaStreamCaptureStatusNone && cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < gi::MAX_DEVICES_SEEN;
+  if (fan && !made[dev]) {
+    bool ok = cudaEventCreateWithFlags(&fork_ev[dev], cudaEventDisableTiming) == cudaSuccess;
+    for (int i = 0; ok && i < SIDE; ++i)
+      ok = cudaStreamCreateWithFlags(&side[dev][i], cudaStreamNonBlocking) == cudaSuccess &&
+           cudaEventCreateWithFlags(&join_ev[dev][i], cudaEventDisableTiming) == cudaSuccess;
+    if (!ok) { cudaGetLastError(); fan = false; } else made[dev] = true;
+  }
+  if (fan) {
+    if (cudaEventRecord(fork_ev[dev], main_stream) != cudaSuccess) return gi::fail(GI_ERR_CUDA, "experts on tensor cores: fork");
+    for (int i = 0; i < SIDE; ++i) cudaStreamWaitEvent(side[dev][i], fork_ev[dev], 0);
+  }
+  int turn = 0;
   for (int e = 0; e < experts; ++e) {
     const int lo = host_offsets[e], m = host_offsets[e + 1] - lo;
-    if (m <= 0) continue;
+    if (m <= 64) continue;
     const __nv_bfloat16* wgu = (const __nv_bfloat16*)w_gate_up + (size_t)e * gate_up_stride;
     const __nv_bfloat16* wd = (const __nv_bfloat16*)w_down + (size_t)e * down_stride;
-    int rc;
-    if (m <= 64) {
-      rc = gi_gemm_stream_bf16(h + (size_t)lo * f, GI_SKINNY_SWIGLU, a + (size_t)lo * width, wgu, scratch, counters, n_counters, m,
-                               2 * f, width, width, width, f, -1, stream);
-      if (rc == GI_OK)
-        rc = gi_gemm_stream_bf16(out + (size_t)lo * width, GI_SKINNY_STORE_F32, h + (size_t)lo * f, wd, scratch, counters, n_counters,
-                                 m, width, f, f, f, width, -1, stream);
-    } else {
-      rc = gi_gemm_tc_bf16(h + (size_t)lo * f, GI_TC_SWIGLU, a + (size_t)lo * width, wgu, m, 2 * f, width, width, width, f, 256, stream);
-      if (rc == GI_OK)
-        rc = gi_gemm_tc_bf16(out + (size_t)lo * width, GI_TC_STORE_F32, h + (size_t)lo * f, wd, m, width, f, f, f, width, 256, stream);
+    cudaStream_t s = fan ? side[dev][turn++ % SIDE] : main_stream;
+    // narrower tiles where wide ones would leave most SMs without one
+    const int row_tiles = (m + 127) / 128;
+    const int tile_up = row_tiles * ((2 * f + 255) / 256) < 64 ? 128 : 256, tile_down = row_tiles * ((width + 255) / 256) < 64 ? 128 : 256;
+    int rc = gi_gemm_tc_bf16(h + (size_t)lo * f, GI_TC_SWIGLU, a + (size_t)lo * width, wgu, m, 2 * f, width, width, width, f, tile_up, s);
+    if (rc == GI_OK)
+      rc = gi_gemm_tc_bf16(out + (size_t)lo * width, GI_TC_STORE_F32, h + (size_t)lo * f, wd, m, width, f, f, f, width, tile_down, s);
+    if (rc != GI_OK) return rc;
+  }
+  if (fan) {
+    for (int i = 0; i < SIDE; ++i) {
+      cudaEventRecord(join_ev[dev][i], side[dev][i]);
+      cudaStreamWaitEvent(main_stream, join_ev[dev][i], 0);
     }
+    if (cudaGetLastError() != cudaSuccess) return gi::fail(GI_ERR_CUDA, "experts on tensor cores: join");
+  }
+  for (int e = 0; e < experts; ++e) {
+    const int lo = host_offsets[e], m = host_offsets[e + 1] - lo;
+    if (m <= 0 || m > 64) continue;
+    const __nv_bfloat16* wgu = (const __nv_bfloat16*)w_gate_up + (size_t)e * gate_up_stride;
+    const __nv_bfloat16* wd = (const __nv_bfloat16*)w_down + (size_t)e * down_stride;
+    int rc = gi_gemm_stream_bf16(h + (size_t)lo * f, GI_SKINNY_SWIGLU, a + (size_t)lo * width, wgu, scratch, counters, n_counters, m,
+                                 2 * f, width, width, width, f, -1, main_stream);
+    if (rc == GI_OK)
+      rc = gi_gemm_stream_bf16(out + (size_t)lo * width, GI_SKINNY_STORE_F32, h + (size_t)lo * f, wd, scratch, counters, n_counters,
+                               m, width, f, f, f, width, -1, main_stream);
     if (rc != GI_OK) return rc;
   }
   return GI_OK;
