@@ -300,6 +300,11 @@ int gi_attn_prefill_t5(void* out, long ldo, const void* q, long ldq, long q_rows
                        void* stream);
 // query tiles two to a block (the i-th from the end with the i-th from the start): 0 never, 1 where the launch then
 // is one round of blocks (default), 2 always
+// gi_attn_prefill_t5 with a cap on the scores, a sink per head and chunks of positions (see gi_attn_prefill_generic_ex).
+int gi_attn_prefill_t5_ex(void* out, long ldo, const void* q, long ldq, long q_rows, const void* kcache, const void* vcache,
+                          long cache_pages, const int* block_table, int max_pages, const int* cu_seqlens,
+                          const int* seq_slots, const int* seq_pos0, int n_seqs, int max_q_len, int n_heads, int n_kv, int hd,
+                          float scale, int window, float softcap, const float* sinks, int chunk, void* stream);
 int gi_attn_prefill_t5_pairing(int mode);
 int gi_attn_prefill_t5_status(int* status);
 // bfloat16, head size 64 or 128: the same operation as gi_attn_decode_generic, on tensor cores

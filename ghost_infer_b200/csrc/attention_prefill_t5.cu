@@ -81,7 +81,7 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out, long ldo,
                        const int* __restrict__ block_table, int max_pages, const int* __restrict__ cu_seqlens,
                        const int* __restrict__ seq_slots, const int* __restrict__ seq_pos0, int n_heads, int n_kv, float scale,
-                       int window, int q_tiles, int paired) {
+                       int window, int q_tiles, int paired, float softcap, const float* __restrict__ sinks, int chunk) {
   constexpr int HALVES = HD / 64;
   constexpr uint32_t Q_BYTES = HALVES * Q_HALF, KV_BYTES = HALVES * KV_HALF;
   // instruction descriptors: float accumulator, bfloat16 operands, M 128; S = Q K^T has N 64 and both operands K-major,
@@ -168,6 +168,7 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const int p_last = pos0 + q0 + rows_here - 1;
   int t_first = 0;
   if (window > 0) t_first = max(0, pos0 + q0 - window + 1);
+  if (chunk > 0) t_first = max(t_first, ((pos0 + q0) / chunk) * chunk);     // chunks of positions: see the row warps
   const int kt_begin = (t_first / BKV) * BKV;
   const int n_tiles = (p_last - kt_begin) / BKV + 1;
 
@@ -267,7 +268,15 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int row = warp * 32 + lane;                 // query row = tensor-memory lane
     const int p_row = pos0 + q0 + row;                // its position
     const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-    const float sl2 = scale * 1.4426950408889634f;
+    // Options of some designs' attention, each off at its neutral value.  A cap on the scores, s <- cap tanh(s / cap):
+    // the raw products become capped scores in base-2 units as soon as they are read, and the scale that follows is 1.
+    // Chunks of positions: a row sees keys from the first position of its own chunk floor(pos / chunk) on; a tile needs
+    // no mask only if it lies inside the chunk of the block's last row too.  A sink per head joins the denominator at
+    // the end.
+    const float sl2 = softcap > 0.f ? 1.0f : scale * 1.4426950408889634f;
+    const float cap_in = softcap > 0.f ? scale / softcap : 0.f, cap_out = softcap * 1.4426950408889634f;
+    const int c_lo_row = chunk > 0 ? (p_row / chunk) * chunk : 0;
+    const int c_lo_last = chunk > 0 ? ((pos0 + q0 + BQ - 1) / chunk) * chunk : 0;
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
     for (int j = 0; j < n_tiles && ok; ++j) {
@@ -284,7 +293,14 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       // scores -> probabilities.  A tile every row of the block sees in full needs no mask: one maximum, then one
       // fused multiply-add, one exponential and one addition per score.  Tiles on the diagonal (or at a window's
       // edge) take the masked path.
-      const bool interior = (kt + BKV - 1 <= pos0 + q0) && kt >= t_first && (window <= 0 || kt > pos0 + q0 + BQ - 1 - window);
+      const bool interior = (kt + BKV - 1 <= pos0 + q0) && kt >= t_first && (window <= 0 || kt > pos0 + q0 + BQ - 1 - window) &&
+                            kt >= c_lo_last;
+      if (softcap > 0.f) {
+#pragma unroll
+        for (int q = 0; q < 2; ++q)
+#pragma unroll
+          for (int c = 0; c < 32; ++c) sr[q][c] = __float_as_uint(cap_out * gi::tanh_fast(__uint_as_float(sr[q][c]) * cap_in));
+      }
       float tmax = -INFINITY;
       if (interior) {
 #pragma unroll
@@ -298,7 +314,7 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
           for (int c = 0; c < 32; ++c) {
             const int key = kt + q * 32 + c;
-            const bool vis = key <= p_row && key >= t_first && (window <= 0 || key > p_row - window);
+            const bool vis = key <= p_row && key >= t_first && (window <= 0 || key > p_row - window) && key >= c_lo_row;
             const float v = vis ? __uint_as_float(sr[q][c]) : -INFINITY;
             sr[q][c] = __float_as_uint(v);
             tmax = fmaxf(tmax, v * sl2);
@@ -377,7 +393,16 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     if (ok) ok = mbar_wait(kv_empty0 + 8 * ((n_tiles - 1) & 1), (uint32_t)(((n_tiles - 1) >> 1) & 1), 3, &g_attn_status);
     tc_fence_after();
     if (ok) {
-      const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+      float a_sink = 1.0f;
+      if (sinks != nullptr) {
+        // one more term of the denominator, with no value behind it (m_run is the reference point of the row's
+        // exponentials, in base-2 units; the sum is rebased to the larger of it and the sink)
+        const float sk = sinks[h] * 1.4426950408889634f;
+        const float m_f = fmaxf(m_run, sk);
+        a_sink = (m_run == -INFINITY) ? 0.f : ex2(m_run - m_f);
+        l_run = l_run * a_sink + ex2(sk - m_f);
+      }
+      const float inv = l_run > 0.f ? a_sink / l_run : 0.f;
       __nv_bfloat16* orow_g = out + (size_t)(tok0 + q0 + row) * ldo + (size_t)h * HD;
 #pragma unroll 1
       for (int c = 0; c < HD / 32; ++c) {
@@ -415,7 +440,7 @@ attn_prefill_t5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 template <int HD>
 int launch_t5(dim3 grid, cudaStream_t stream, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, __nv_bfloat16* out,
               long ldo, const int* block_table, int max_pages, const int* cu_seqlens, const int* seq_slots, const int* seq_pos0,
-              int n_heads, int n_kv, float scale, int window, int q_tiles, int paired) {
+              int n_heads, int n_kv, float scale, int window, int q_tiles, int paired, float softcap, const float* sinks, int chunk) {
   constexpr size_t smem = (HD / 64) * (Q_HALF + 4 * KV_HALF) + 12 * 8 + 16;
   static bool configured[gi::MAX_DEVICES_SEEN] = {false};
   int dev;
@@ -425,7 +450,7 @@ int launch_t5(dim3 grid, cudaStream_t stream, const CUtensorMap& mq, const CUten
     if (dev >= 0) configured[dev] = true;
   }
   return gi::check(gi::launch(attn_prefill_t5_kernel<HD>, grid, dim3(THREADS), smem, stream, mq, mk, mv, out, ldo, block_table, max_pages,
-                              cu_seqlens, seq_slots, seq_pos0, n_heads, n_kv, scale, window, q_tiles, paired),
+                              cu_seqlens, seq_slots, seq_pos0, n_heads, n_kv, scale, window, q_tiles, paired, softcap, sinks, chunk),
                    "attention prefill (tcgen05)");
 }
 
@@ -435,7 +460,19 @@ extern "C" int gi_attn_prefill_t5(void* out, long ldo, const void* q, long ldq, 
                                   const void* vcache, long cache_pages, const int* block_table, int max_pages,
                                   const int* cu_seqlens, const int* seq_slots, const int* seq_pos0, int n_seqs,
                                   int max_q_len, int n_heads, int n_kv, int hd, float scale, int window, void* stream) {
+  return gi_attn_prefill_t5_ex(out, ldo, q, ldq, q_rows, kcache, vcache, cache_pages, block_table, max_pages, cu_seqlens, seq_slots,
+                               seq_pos0, n_seqs, max_q_len, n_heads, n_kv, hd, scale, window, 0.f, nullptr, 0, stream);
+}
+
+// The same with a cap on the scores (s <- cap tanh(s / cap); 0: none), a sink per head (float[heads] or null) and chunks of
+// positions (0: none); keys and values of one size, 64 or 128.
+extern "C" int gi_attn_prefill_t5_ex(void* out, long ldo, const void* q, long ldq, long q_rows, const void* kcache,
+                                     const void* vcache, long cache_pages, const int* block_table, int max_pages,
+                                     const int* cu_seqlens, const int* seq_slots, const int* seq_pos0, int n_seqs,
+                                     int max_q_len, int n_heads, int n_kv, int hd, float scale, int window, float softcap,
+                                     const float* sinks, int chunk, void* stream) {
   if (n_seqs <= 0 || max_q_len <= 0) return GI_OK;
+  if (chunk < 0 || softcap < 0.f) return gi::fail(GI_ERR_ARG, "attention: a chunk or a cap cannot be negative");
   if (hd != 64 && hd != 128) return gi::fail(GI_ERR_UNSUPPORTED, "attention prefill (tcgen05): head size %d, only 64 and 128", hd);
   if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0)
     return gi::fail(GI_ERR_ARG, "attention: %d heads do not divide into %d kv heads", n_heads, n_kv);
@@ -462,9 +499,9 @@ extern "C" int gi_attn_prefill_t5(void* out, long ldo, const void* q, long ldq, 
   dim3 grid(n_heads, n_seqs, paired ? (q_tiles + 1) / 2 : q_tiles);
   if (hd == 128)
     return launch_t5<128>(grid, (cudaStream_t)stream, mq, mk, mv, (__nv_bfloat16*)out, ldo, block_table, max_pages, cu_seqlens, seq_slots,
-                          seq_pos0, n_heads, n_kv, scale, window, q_tiles, paired);
+                          seq_pos0, n_heads, n_kv, scale, window, q_tiles, paired, softcap, sinks, chunk);
   return launch_t5<64>(grid, (cudaStream_t)stream, mq, mk, mv, (__nv_bfloat16*)out, ldo, block_table, max_pages, cu_seqlens, seq_slots,
-                       seq_pos0, n_heads, n_kv, scale, window, q_tiles, paired);
+                       seq_pos0, n_heads, n_kv, scale, window, q_tiles, paired, softcap, sinks, chunk);
 }
 
 // Query tiles two to a block: 0 never, 1 where the launch then is one round of blocks (default), 2 always; for

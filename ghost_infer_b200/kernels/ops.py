@@ -61,6 +61,7 @@ def _bind():
         "gi_attn_prefill_tc": [P, L, P, L, P, P, P, I, P, P, P, I, I, I, I, I, F, I, P],
         "gi_attn_prefill_t5": [P, L, P, L, L, P, P, L, P, I, P, P, P, I, I, I, I, I, F, I, P],
         "gi_attn_prefill_t5_status": [P],
+        "gi_attn_prefill_t5_ex": [P, L, P, L, L, P, P, L, P, I, P, P, P, I, I, I, I, I, F, I, F, P, I, P],
         "gi_attn_decode_tc": [P, L, P, P, P, L, P, P, P, I, P, P, I, I, I, I, F, I, I, P],
         "gi_attn_decode_tc_ex": [P, L, P, P, P, L, P, P, P, I, P, P, I, I, I, I, F, I, I, I, P],
         "gi_attn_decode_tc_merged": [P, L, P, P, P, I, P, L, P, P, P, I, P, P, I, I, I, I, F, I, I, I, I, I, P],
@@ -896,9 +897,11 @@ def attn_prefill_tc(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
 def attn_prefill_t5(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_table: torch.Tensor,
                     cu_seqlens: torch.Tensor, seq_slots: torch.Tensor, seq_pos0: torch.Tensor, n_seqs: int,
                     max_q_len: int, n_heads: int, n_kv: int, head_dim: int, scale: float,
-                    window: Optional[int], out: torch.Tensor) -> torch.Tensor:
-    """As attn_prefill_generic, for bfloat16 and head size 64 or 128, on tcgen05 tensor cores with TMA-fed operands.
-    `q` is the whole packed [tokens, (H + 2 KV) * head_dim] matrix (its first columns are the queries)."""
+                    window: Optional[int], out: torch.Tensor, *, softcap: float = 0.0, sinks: Optional[torch.Tensor] = None,
+                    chunk: Optional[int] = None) -> torch.Tensor:
+    """As attn_prefill_generic, for bfloat16 and head size 64 or 128 (keys and values alike), on tcgen05 tensor cores with
+    TMA-fed operands.  `q` is the whole packed [tokens, (H + 2 KV) * head_dim] matrix (its first columns are the queries).
+    `softcap`, `sinks`, `chunk`: as `attn_prefill_generic`'s."""
     lib = _bind()
     _cuda(q, "queries")
     ldq, ldo = _rows(q, "queries"), _rows(out, "attention output")
@@ -906,11 +909,11 @@ def attn_prefill_t5(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
         raise KernelError("the tcgen05 prefill attention takes bfloat16 queries, cache and output")
     if not kcache.is_contiguous() or not vcache.is_contiguous() or q.shape[1] != (n_heads + 2 * n_kv) * head_dim:
         raise KernelError("the tcgen05 prefill attention takes the packed q/k/v rows and contiguous cache pages")
-    _check(lib, lib.gi_attn_prefill_t5(
+    _check(lib, lib.gi_attn_prefill_t5_ex(
         out.data_ptr(), ldo, q.data_ptr(), ldq, q.shape[0], kcache.data_ptr(), vcache.data_ptr(), kcache.shape[0],
         _i32(block_table, "block table"), block_table.shape[1], _i32(cu_seqlens, "cu_seqlens"),
         _i32(seq_slots, "slots"), _i32(seq_pos0, "start positions"), n_seqs, max_q_len, n_heads, n_kv, head_dim,
-        float(scale), int(window or 0), _stream()))
+        float(scale), int(window or 0), float(softcap or 0.0), _sinks_ptr(sinks, n_heads), int(chunk or 0), _stream()))
     return out
 
 
@@ -1287,6 +1290,14 @@ def attention_general(qkv: torch.Tensor, memory, step, n_heads: int, n_kv: int, 
         return attn_decode_generic(qkv, memory.k, memory.v, memory.block_table, step.seq_slots, step.seq_lens, step.n_seqs,
                                    n_heads, n_kv, head_dim, scale, window, n_splits, out, part_o, part_ml, own_tiles=own_tiles,
                                    **opts)
+    if (TUNE["attn_general_tc"] and TUNE["attn_prefill_tcgen05"] and qkv.dtype == torch.bfloat16 and memory.k.dtype == torch.bfloat16
+            and head_dim == v_dim and head_dim in (64, 128) and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0
+            and qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0 and qkv.shape[1] == (n_heads + 2 * n_kv) * head_dim
+            and memory.k.is_contiguous() and memory.v.is_contiguous()):
+        # keys and values of one of the two sizes the tcgen05 kernel takes: scores and output in tensor memory
+        return attn_prefill_t5(qkv, memory.k, memory.v, memory.block_table, step.cu_seqlens, step.seq_slots, step.seq_pos0,
+                               step.n_seqs, step.max_q_len, n_heads, n_kv, head_dim, scale, window, out, softcap=softcap,
+                               sinks=sinks, chunk=chunk)
     if (TUNE["attn_general_tc"] and qkv.dtype == torch.bfloat16 and memory.k.dtype == torch.bfloat16 and head_dim % 8 == 0
             and v_dim % 8 == 0 and head_dim <= 128 and v_dim <= 128 and qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0
             and out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0):

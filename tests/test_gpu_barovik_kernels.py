@@ -84,6 +84,8 @@ CASES = [
     (6, 2, 40, 72, None, True, None, 70),
     (3, 3, 128, 128, 5.0, False, 33, None),
     (8, 1, 24, 8, None, False, None, None),
+    (4, 2, 64, 64, 12.0, True, 150, None),     # equal sizes of 64 or 128: the tcgen05 prompt kernel
+    (2, 1, 128, 128, None, True, None, 90),
 ]
 
 
