@@ -75,7 +75,13 @@ CFG_A16 = json.loads(json.dumps(CFG_A))
 for _l in CFG_A16["layers"]:
     if _l["mlp"] and _l["mlp"]["kind"] == "moe":
         _l["mlp"]["router"]["top"] = _l["mlp"]["router"]["experts"]
-CONFIGS = {"A": CFG_A, "A16": CFG_A16, "B": CFG_B}
+# Keys and values of 64 values each: the sizes for which prompts run on the tcgen05 attention kernel in 16 bits.
+CFG_C = model_cfg(128, 150, [
+    layer("attention", attn(4, 2, 64, 64, 50, 0.2, cap=15.0), dense(96)),
+    layer("mamba2", ssm(2, 32, 16, 1, 4, 1), moe(4, 4, 32, shared=32)),
+    layer("attention", attn(4, 2, 64, 64, 50, 0.2, cap=15.0), None),
+])
+CONFIGS = {"A": CFG_A, "A16": CFG_A16, "B": CFG_B, "C": CFG_C}
 _made = {}
 
 
@@ -87,7 +93,7 @@ def made(name):
         # sharp scores: an edge or a sink that is off shows in the logits (not for the model that is only run in 16
         # bits: sharp scores also multiply what the rounding of queries and keys does to the softmax)
         for k in w:
-            if name != "A16" and (k.endswith("mix.q") or k.endswith("mix.k")):
+            if name not in ("A16", "C") and (k.endswith("mix.q") or k.endswith("mix.k")):
                 w[k] = w[k] * 2.0
         _made[name] = (cfg, w, {k: torch.from_numpy(np.asarray(v, dtype=np.float32)).to(torch.bfloat16) for k, v in w.items()})
     return _made[name]
@@ -203,7 +209,8 @@ def test_routed_experts_in_bfloat16():
 
 
 # ---- whole prompts, tails token by token, portions -----------------------------------------------------------------
-@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("A16", "bfloat16"), ("B", "float32"), ("B", "bfloat16")])
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("A16", "bfloat16"), ("B", "float32"), ("B", "bfloat16"), ("C", "bfloat16"),
+                                        ("C", "float32")])
 def test_whole_prompt(name, dtype):
     eng = engine_for(name, dtype)
     for n, seed in ((1, 1), (2, 2), (150, 3)):       # the first tokens of a sequence, and chunk and page borders
@@ -212,7 +219,7 @@ def test_whole_prompt(name, dtype):
 
 
 @pytest.mark.parametrize("name,dtype,graph", [("A", "float32", True), ("A16", "bfloat16", True), ("B", "float32", False),
-                                              ("B", "float32", True)])
+                                              ("B", "float32", True), ("C", "bfloat16", True)])
 def test_prompt_then_token_by_token(name, dtype, graph):
     """Decoding crosses chunk edges (every 7 or 24 positions), a page border (64, 128) and the state's every step."""
     eng = engine_for(name, dtype)
@@ -237,7 +244,7 @@ def test_decoding_from_the_first_token():
     check(np.concatenate(rows, 0), plain("B", t), "float32")
 
 
-@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "float32"), ("A16", "bfloat16")])
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "float32"), ("A16", "bfloat16"), ("C", "bfloat16")])
 def test_portions_of_several_sizes(name, dtype):
     eng = engine_for(name, dtype)
     t = toks(name, 200, 13)
