@@ -119,3 +119,25 @@ def test_plain_mechanisms_on_small_cases_worked_by_hand():
     p = np.exp([3.0, 2.0]) / np.exp([3.0, 2.0]).sum()
     assert np.allclose(pb.routed_ff(np.array([[1.0]]), wr, mlp), p[0] * pb.silu(1.0) + p[1] * pb.silu(2.0))
     assert abs(pb.gelu_tanh(np.array(1.0)) - 0.8411919906) < 1e-9
+
+
+def test_command_line_makes_and_lists_a_model_folder(tmp_path, capsys):
+    import json
+    from ghost_infer_b200 import cli
+    from ghost_infer_b200.weights.safetensors_io import SafetensorsFile
+    cfg_file = tmp_path / "config.json"
+    cfg_file.write_text(json.dumps(CFG))
+    out = tmp_path / "model"
+    assert cli.main(["random", str(cfg_file), str(out), "--seed", "3"]) == 0
+    names = set(SafetensorsFile(str(out / "model.safetensors")).names())
+    assert names == {w.name for w in Model.from_config_dict(CFG).weight_manifest()}
+    assert cli.main(["inspect", str(out)]) == 0
+    text = capsys.readouterr().out
+    assert "l0.mix.A_log" in text and f"{len(names)} tensors" in text
+    # a file may carry tensors for what the configuration switches off; anything else is refused
+    from ghost_infer_b200.weights.loader import WeightsError, load_model_tensors
+    model = Model.from_config_dict(CFG)
+    assert "l2.mix.vmix" in model.ignorable_tensors() and "l0.norm2" in model.ignorable_tensors()
+    load_model_tensors(str(out), model.weight_manifest(), model.ignorable_tensors())
+    with pytest.raises(WeightsError):
+        load_model_tensors(str(out), [w for w in model.weight_manifest() if w.name != "head"], model.ignorable_tensors())
