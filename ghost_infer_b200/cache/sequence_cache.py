@@ -34,12 +34,14 @@ class CacheRequest:
     """What a mixer wants kept per token.  kind "full": every position stays visible;
     kind "window": only the last `window` positions are ever read again; kind "chunk": only positions p with
     floor(p / window) equal to that of the reader's own position.  `v_head_dim`: the values' width when it is not
-    the keys' `head_dim`."""
+    the keys' `head_dim`.  `values_in_keys`: nothing is stored for the values; a position's value is the leading
+    `v_head_dim` numbers of its key row (a latent that serves as both), and `LayerMemory.v` is None."""
     kind: str
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     v_head_dim: Optional[int] = None
+    values_in_keys: bool = False
 
     def __post_init__(self):
         if self.kind not in ("full", "window", "chunk"):
@@ -48,6 +50,8 @@ class CacheRequest:
             raise ValueError(f"a {self.kind} cache needs a positive size")
         if self.v_head_dim is not None and self.v_head_dim < 1:
             raise ValueError("the values' width must be positive")
+        if self.values_in_keys and self.value_dim > self.head_dim:
+            raise ValueError("values that live in the key rows cannot be wider than the keys")
 
     @property
     def value_dim(self) -> int:
@@ -96,7 +100,7 @@ class _Group:
         # zero-filled once: rows past a sequence's length are never read, but the padding rows of
         # fixed-size launches read the trash page, which must hold finite numbers
         self.k = torch.zeros(shape, dtype=self.dtype, device=self.device)
-        self.v = torch.zeros(shape[:-1] + (r.value_dim,), dtype=self.dtype, device=self.device)
+        self.v = None if r.values_in_keys else torch.zeros(shape[:-1] + (r.value_dim,), dtype=self.dtype, device=self.device)
         self.table_dev = torch.zeros(self.table_host.shape, dtype=torch.int32, device=self.device)
 
 
@@ -148,7 +152,8 @@ class SequenceCache:
         total = 0
         esz = torch.empty((), dtype=self.dtype).element_size()
         for g in self._groups:
-            total += len(g.entries) * g.request.num_kv_heads * (g.request.head_dim + g.request.value_dim) * esz
+            stored = g.request.head_dim + (0 if g.request.values_in_keys else g.request.value_dim)
+            total += len(g.entries) * g.request.num_kv_heads * stored * esz
         return total
 
     def state_bytes_per_sequence(self) -> int:
@@ -306,5 +311,5 @@ class SequenceCache:
         if gi is None:
             return LayerMemory(None, None, None, None, writes, state)
         g, idx = gi
-        return LayerMemory(g.k[idx], g.v[idx], g.table_dev, g.request.window if g.request.kind == "window" else None,
+        return LayerMemory(g.k[idx], g.v[idx] if g.v is not None else None, g.table_dev, g.request.window if g.request.kind == "window" else None,
                            writes, state, g.request.window if g.request.kind == "chunk" else None)

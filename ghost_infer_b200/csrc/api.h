@@ -203,6 +203,45 @@ int gi_attn_decode_generic_ex(void* out, long ldo, float* part_o, float* part_ml
                               float scale, int window, int n_splits, int own_tiles, int hdv, float softcap,
                               const float* sinks, int chunk, void* stream);
 
+// The same two with the value rows `v_row_stride` numbers apart instead of hdv (a cache whose values are the leading hdv
+// numbers of its key rows passes the keys as values and the keys' row length here); keys up to 640 and values up to 512 wide.
+int gi_attn_prefill_generic_ex2(void* out, long ldo, const void* q, long ldq, int dtype, const void* kcache,
+                                const void* vcache, const int* block_table, int max_pages, const int* cu_seqlens,
+                                const int* seq_slots, const int* seq_pos0, int n_seqs, int max_q_len, int n_heads,
+                                int n_kv, int hd, float scale, int window, int hdv, float softcap, const float* sinks,
+                                int chunk, long v_row_stride, void* stream);
+int gi_attn_decode_generic_ex2(void* out, long ldo, float* part_o, float* part_ml, const void* q, long ldq, int dtype,
+                               const void* kcache, const void* vcache, const int* block_table, int max_pages,
+                               const int* seq_slots, const int* seq_lens, int n_seqs, int n_heads, int n_kv, int hd,
+                               float scale, int window, int n_splits, int own_tiles, int hdv, float softcap,
+                               const float* sinks, int chunk, long v_row_stride, void* stream);
+
+// ---- layers with a low-rank latent in place of keys and values per head, and what their feed-forwards add.
+// y = (x - mean) / sqrt(var + eps) * w per row, 32-bit statistics; `rows` (optional) picks the rows of x.
+int gi_layernorm(void* out, int out_dtype, const float* x, const void* w, int w_dtype, const int* rows, int n_rows, int d,
+                 float eps, void* stream);
+// out[t, :f] = act(in[t, :f] + bias) (bias optional; act 0: none, 1: relu squared); with `residual` [n_rows, d] also
+// residual[t, :] += res_bias in the same launch.
+int gi_bias_act(void* out, const void* in, int dtype, long ld_in, const void* bias, int w_dtype, int n_rows, int f, int act,
+                float* residual, const void* res_bias, int d, void* stream);
+// in[t] = [query latent (rq) | key/value latent (r) | rotary key part (dr)]: cq[t] = rmsnorm(query latent) * wq (skipped
+// when rq is 0); the cache row of token t, [r + dr] numbers in pages [page][64][r + dr], = [rmsnorm(latent) * wc | key part
+// with its first `rot` numbers turned in neighbouring pairs by table[t]].
+int gi_latent_prepare(void* cq, const void* in, int dtype, long ld, const void* wq, const void* wc, int w_dtype, float eps,
+                      const float* table, int rot, const int* positions, const int* slots, const int* block_table, int max_pages,
+                      void* kcache, int n_tokens, int rq, int r, int dr, int write_cache, void* stream);
+// qa[t, h, r : r + dr] = q[t, h, dn : dn + dr] with its first `rot` numbers turned (q rows [heads][dn + dr], qa rows
+// [heads][r + dr]).
+int gi_latent_query_rot(void* qa, long ldqa, const void* q, long ldq, int dtype, const float* table, int rot, int n_tokens,
+                        int n_heads, int dn, int dr, int r, void* stream);
+// out[t, h * ohs + n] = sum_k a[t, h * ahs + k] * w[h * whs + n * ldw + k * kstride], n < N, k < K, for every head h; out has
+// a's type.  tensor_cores: bfloat16 operands with kstride 1 take `mma.sync`.
+int gi_bmm_heads(void* out, long ldo, long ohs, const void* a, long lda, long ahs, int dtype, const void* w, int w_dtype,
+                 long whs, long ldw, long kstride, int M, int N, int K, int heads, int tensor_cores, void* stream);
+// table[t, i] = magnitude * (cos, sin)(positions[t] * inv_freq[i])
+int gi_rope_table_scaled(float* table, const int* positions, const float* inv_freq, int n_tokens, int rot, float magnitude,
+                         void* stream);
+
 // The prompt operation of gi_attn_prefill_generic_ex on tensor cores: bfloat16, key and value sizes multiples of 8 up to 128.
 int gi_attn_prefill_tc_ex(void* out, long ldo, const void* q, long ldq, const void* kcache, const void* vcache,
                           const int* block_table, int max_pages, const int* cu_seqlens, const int* seq_slots,
@@ -255,6 +294,9 @@ int gi_mamba2_gate_norm(void* out, int out_dtype, const float* y, const void* pr
 // logits; optional shared gate sg[t] = sigmoid(h . w_sg).  ids int[tokens, top], wts float[tokens, top].
 int gi_moe_route(int* ids, float* wts, float* sgate, const void* h, int dtype, long ldh, const void* w_router,
                  const void* w_sg, int w_dtype, int n_tokens, int width, int experts, int top, void* stream);
+// The same with the kind of weights named: 0 as above; 1: every chosen expert's own sigmoid(logit), not renormalized.
+int gi_moe_route_scored(int* ids, float* wts, float* sgate, const void* h, int dtype, long ldh, const void* w_router,
+                        const void* w_sg, int w_dtype, int n_tokens, int width, int experts, int top, int score_mode, void* stream);
 // plan: a stable counting sort of the tokens' choices by expert.  offsets int[experts + 1]; perm int[entries] (sorted
 // place -> entry t * top + k); inv int[entries] (entry -> sorted place).  scratch: int[(entries + 1023) / 1024 *
 // experts * 2 + entries].
@@ -270,12 +312,20 @@ int gi_moe_gather_rows(void* out, const void* in, int dtype, long ld_in, const i
                        void* stream);
 int gi_moe_gemm_down(float* out, const void* a, int dtype, long lda, const void* w, int w_dtype, long w_stride,
                      const int* offsets, int entries, int experts, int n, int k, void* stream);
+// gi_moe_gemm_down with a choice of what is stored: act_out 0: the sums as float; 1: relu(sum)^2 in the rows' type (the
+// hidden layer of an ungated expert).
+int gi_moe_gemm_rows(void* out, const void* a, int dtype, long lda, const void* w, int w_dtype, long w_stride,
+                     const int* offsets, int entries, int experts, int n, int k, int act_out, void* stream);
+// gi_moe_gather_rows with every gathered row multiplied by scale[perm[r]] (one float per entry; null: as they are).
+int gi_moe_gather_rows_scaled(void* out, const void* in, int dtype, long ld_in, const int* perm, const float* scale,
+                              int entries, int top, int width, void* stream);
 // The experts of a prompt step through the tcgen05 products, one expert's stretch of the sorted rows after another, from
 // offsets on the HOST (int[experts + 1]); bfloat16, gate and up rows interleaved.  hidden: bfloat16 [entries, f] scratch.
 int gi_moe_experts_tc(float* out, void* hidden, const void* rows, const void* w_gate_up, long gate_up_stride,
                       const void* w_down, long down_stride, const int* host_offsets, int experts, int width, int f,
                       float* scratch, int* counters, int n_counters, void* stream);
-// residual[t, :] += sum_k wts[t, k] * down[inv[t * top + k], :] (k in order) + sgate[t] * shared[t, :] (if given).
+// residual[t, :] += sum_k wts[t, k] * down[inv[t * top + k], :] (k in order; wts null: every weight 1) + sgate[t] *
+// shared[t, :] (if given).
 int gi_moe_combine(float* residual, const float* down, const int* inv, const float* wts, const float* shared,
                    const float* sgate, int n_tokens, int width, int top, void* stream);
 

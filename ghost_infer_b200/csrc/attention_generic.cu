@@ -31,7 +31,7 @@ attn_prefill_kernel(T* __restrict__ out, long ldo, const T* __restrict__ q, long
                     const T* __restrict__ vcache, const int* __restrict__ block_table, int max_pages,
                     const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slots,
                     const int* __restrict__ seq_pos0, int n_heads, int n_kv, int hd, float scale, int window,
-                    int hdv, float softcap, const float* __restrict__ sinks, int chunk) {
+                    int hdv, float softcap, const float* __restrict__ sinks, int chunk, long vrs) {
   extern __shared__ float smem[];
   const int ldk = hd + 1, ldv = hdv + 1;
   float* Qs = smem;                  // [QT][hd+1]
@@ -70,18 +70,18 @@ attn_prefill_kernel(T* __restrict__ out, long ldo, const T* __restrict__ q, long
     __syncthreads();
     const int page = block_table[(size_t)slot * max_pages + kt / PAGE_TOKENS];
     const size_t row0 = ((size_t)page * n_kv + kvh) * PAGE_TOKENS + (kt % PAGE_TOKENS);
-    const size_t base = row0 * hd, base_v = row0 * hdv;
+    const size_t base = row0 * hd, base_v = row0 * (size_t)vrs;
     for (int idx = tid; idx < KT * hd; idx += 128) {
       const int j = idx / hd, d = idx % hd;
       const bool live = kt + j <= p_last && kt + j >= t_first;   // rows no query here sees are not read
       Ks[j * ldk + d] = live ? gi::ldf(kcache + base + (size_t)j * hd + d) : 0.f;
-      if (hdv == hd) Vs[j * ldv + d] = live ? gi::ldf(vcache + base_v + (size_t)j * hdv + d) : 0.f;
+      if (hdv == hd) Vs[j * ldv + d] = live ? gi::ldf(vcache + base_v + (size_t)j * vrs + d) : 0.f;
     }
     if (hdv != hd) {
       for (int idx = tid; idx < KT * hdv; idx += 128) {
         const int j = idx / hdv, d = idx % hdv;
         const bool live = kt + j <= p_last && kt + j >= t_first;
-        Vs[j * ldv + d] = live ? gi::ldf(vcache + base_v + (size_t)j * hdv + d) : 0.f;
+        Vs[j * ldv + d] = live ? gi::ldf(vcache + base_v + (size_t)j * vrs + d) : 0.f;
       }
     }
     __syncthreads();
@@ -164,7 +164,7 @@ attn_decode_kernel(T* __restrict__ out, long ldo, float* __restrict__ part_o, fl
                    const T* __restrict__ q, long ldq, const T* __restrict__ kcache, const T* __restrict__ vcache,
                    const int* __restrict__ block_table, int max_pages, const int* __restrict__ seq_slots,
                    const int* __restrict__ seq_lens, int n_heads, int n_kv, int hd, float scale, int window,
-                   int n_splits, int own_tiles, int hdv, float softcap, const float* __restrict__ sinks, int pos_chunk) {
+                   int n_splits, int own_tiles, int hdv, float softcap, const float* __restrict__ sinks, int pos_chunk, long vrs) {
   extern __shared__ float smem[];
   float* Qs = smem;                       // [GC][hd]
   float* Mo = Qs + GC * hd;               // [4][GC][hdv] warp outputs
@@ -209,7 +209,7 @@ attn_decode_kernel(T* __restrict__ out, long ldo, float* __restrict__ part_o, fl
     const int t0 = t_base + tile * KT;
     const int page = slot >= 0 ? block_table[(size_t)slot * max_pages + t0 / PAGE_TOKENS] : 0;
     const size_t row0 = ((size_t)page * n_kv + kvh) * PAGE_TOKENS + (t0 % PAGE_TOKENS);
-    const size_t base = row0 * hd, base_v = row0 * hdv;
+    const size_t base = row0 * hd, base_v = row0 * (size_t)vrs;
     const int t = t0 + lane;
     const bool ok = t < len && t >= t_first;
     float s[GC];
@@ -244,7 +244,7 @@ attn_decode_kernel(T* __restrict__ out, long ldo, float* __restrict__ part_o, fl
 #pragma unroll
       for (int c = 0; c < DC; ++c) {
         const int d = lane + 32 * c;
-        v[c] = (d < hdv && t0 + j >= t_first) ? gi::ldf(vcache + base_v + (size_t)j * hdv + d) : 0.f;
+        v[c] = (d < hdv && t0 + j >= t_first) ? gi::ldf(vcache + base_v + (size_t)j * vrs + d) : 0.f;
       }
 #pragma unroll
       for (int g = 0; g < GC; ++g) {
@@ -381,7 +381,7 @@ template <typename T>
 int launch_prefill(int dpt, dim3 grid, size_t smem, cudaStream_t s, T* out, long ldo, const T* q, long ldq,
                    const T* kc, const T* vc, const int* bt, int max_pages, const int* cu, const int* slots,
                    const int* pos0, int H, int KV, int hd, float scale, int window, int hdv, float softcap,
-                   const float* sinks, int chunk) {
+                   const float* sinks, int chunk, long vrs) {
 #define GI_PREFILL_CASE(D)                                                                                       \
   case D: {                                                                                                      \
     auto kern = attn_prefill_kernel<T, D>;                                                                       \
@@ -389,7 +389,7 @@ int launch_prefill(int dpt, dim3 grid, size_t smem, cudaStream_t s, T* out, long
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
       if (e != cudaSuccess) return gi::fail(GI_ERR_CUDA, "attention prefill: %s", cudaGetErrorString(e));        \
     }                                                                                                            \
-    kern<<<grid, 128, smem, s>>>(out, ldo, q, ldq, kc, vc, bt, max_pages, cu, slots, pos0, H, KV, hd, scale, window, hdv, softcap, sinks, chunk); \
+    kern<<<grid, 128, smem, s>>>(out, ldo, q, ldq, kc, vc, bt, max_pages, cu, slots, pos0, H, KV, hd, scale, window, hdv, softcap, sinks, chunk, vrs); \
     break;                                                                                                       \
   }
   switch (dpt) {
@@ -398,8 +398,9 @@ int launch_prefill(int dpt, dim3 grid, size_t smem, cudaStream_t s, T* out, long
     GI_PREFILL_CASE(16)
     GI_PREFILL_CASE(32)
     GI_PREFILL_CASE(64)
+    GI_PREFILL_CASE(128)
     default:
-      return gi::fail(GI_ERR_UNSUPPORTED, "attention prefill: head size %d is above 256", hd);
+      return gi::fail(GI_ERR_UNSUPPORTED, "attention prefill: value size %d is above 512", hdv);
   }
 #undef GI_PREFILL_CASE
   return gi::check_launch("attention prefill");
@@ -409,7 +410,7 @@ template <typename T, int GC>
 int launch_decode_dc(int dc, dim3 grid, size_t smem, cudaStream_t s, T* out, long ldo, float* po, float* pml,
                      const T* q, long ldq, const T* kc, const T* vc, const int* bt, int max_pages, const int* slots,
                      const int* lens, int H, int KV, int hd, float scale, int window, int n_splits, int own_tiles,
-                     int hdv, float softcap, const float* sinks, int chunk) {
+                     int hdv, float softcap, const float* sinks, int chunk, long vrs) {
 #define GI_DECODE_CASE(D)                                                                                        \
   case D: {                                                                                                      \
     auto kern = attn_decode_kernel<T, GC, D>;                                                                    \
@@ -417,7 +418,7 @@ int launch_decode_dc(int dc, dim3 grid, size_t smem, cudaStream_t s, T* out, lon
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
       if (e != cudaSuccess) return gi::fail(GI_ERR_CUDA, "attention decode: %s", cudaGetErrorString(e));         \
     }                                                                                                            \
-    kern<<<grid, 128, smem, s>>>(out, ldo, po, pml, q, ldq, kc, vc, bt, max_pages, slots, lens, H, KV, hd, scale, window, n_splits, own_tiles, hdv, softcap, sinks, chunk); \
+    kern<<<grid, 128, smem, s>>>(out, ldo, po, pml, q, ldq, kc, vc, bt, max_pages, slots, lens, H, KV, hd, scale, window, n_splits, own_tiles, hdv, softcap, sinks, chunk, vrs); \
     break;                                                                                                       \
   }
   switch (dc) {
@@ -425,8 +426,9 @@ int launch_decode_dc(int dc, dim3 grid, size_t smem, cudaStream_t s, T* out, lon
     GI_DECODE_CASE(2)
     GI_DECODE_CASE(4)
     GI_DECODE_CASE(8)
+    GI_DECODE_CASE(16)
     default:
-      return gi::fail(GI_ERR_UNSUPPORTED, "attention decode: head size %d is above 256", hd);
+      return gi::fail(GI_ERR_UNSUPPORTED, "attention decode: value size %d is above 512", hdv);
   }
 #undef GI_DECODE_CASE
   return gi::check_launch("attention decode");
@@ -463,20 +465,33 @@ extern "C" int gi_attn_prefill_generic_ex(void* out, long ldo, const void* q, lo
                                           const int* cu_seqlens, const int* seq_slots, const int* seq_pos0, int n_seqs,
                                           int max_q_len, int n_heads, int n_kv, int hd, float scale, int window,
                                           int hdv, float softcap, const float* sinks, int chunk, void* stream) {
+  return gi_attn_prefill_generic_ex2(out, ldo, q, ldq, dtype, kcache, vcache, block_table, max_pages, cu_seqlens, seq_slots,
+                                     seq_pos0, n_seqs, max_q_len, n_heads, n_kv, hd, scale, window, hdv, softcap, sinks, chunk,
+                                     hdv, stream);
+}
+
+extern "C" int gi_attn_prefill_generic_ex2(void* out, long ldo, const void* q, long ldq, int dtype, const void* kcache,
+                                           const void* vcache, const int* block_table, int max_pages,
+                                           const int* cu_seqlens, const int* seq_slots, const int* seq_pos0, int n_seqs,
+                                           int max_q_len, int n_heads, int n_kv, int hd, float scale, int window,
+                                           int hdv, float softcap, const float* sinks, int chunk, long v_row_stride,
+                                           void* stream) {
   if (n_seqs <= 0 || max_q_len <= 0) return GI_OK;
-  if (hdv <= 0 || hdv > 256) return gi::fail(GI_ERR_UNSUPPORTED, "attention: value size %d is outside 1..256", hdv);
+  if (hdv <= 0 || hdv > 512) return gi::fail(GI_ERR_UNSUPPORTED, "attention: value size %d is outside 1..512", hdv);
+  if (v_row_stride < hdv) return gi::fail(GI_ERR_ARG, "attention: value rows %ld apart cannot hold %d values", v_row_stride, hdv);
   if (chunk < 0 || softcap < 0.f) return gi::fail(GI_ERR_ARG, "attention: a chunk or a cap cannot be negative");
   if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0)
     return gi::fail(GI_ERR_ARG, "attention: %d heads do not divide into %d kv heads", n_heads, n_kv);
-  if (hd <= 0 || hd > 256) return gi::fail(GI_ERR_UNSUPPORTED, "attention: head size %d is outside 1..256", hd);
+  if (hd <= 0 || hd > 640) return gi::fail(GI_ERR_UNSUPPORTED, "attention: head size %d is outside 1..640", hd);
   if (n_seqs > 65535 || n_heads > 65535) return gi::fail(GI_ERR_UNSUPPORTED, "attention: more than 65535 sequences or heads in one launch");
   const int dpt = max(4, pow2_at_least((hdv + 3) / 4));
   dim3 grid((max_q_len + QT - 1) / QT, n_heads, n_seqs);
   const size_t smem = ((size_t)(QT + KT) * (hd + 1) + (size_t)KT * (hdv + 1) + (size_t)QT * (KT + 1)) * sizeof(float);
+  if (smem > 227 * 1024) return gi::fail(GI_ERR_UNSUPPORTED, "attention: keys of %d and values of %d numbers do not fit the prompt kernel's shared memory", hd, hdv);
   GI_DISPATCH_DTYPE(dtype, T,
       return (launch_prefill<T>(dpt, grid, smem, (cudaStream_t)stream, (T*)out, ldo, (const T*)q, ldq, (const T*)kcache,
                                 (const T*)vcache, block_table, max_pages, cu_seqlens, seq_slots, seq_pos0, n_heads, n_kv,
-                                hd, scale, window, hdv, softcap, sinks, chunk)));
+                                hd, scale, window, hdv, softcap, sinks, chunk, v_row_stride)));
   return GI_OK;
 }
 
@@ -496,13 +511,25 @@ extern "C" int gi_attn_decode_generic_ex(void* out, long ldo, float* part_o, flo
                                          int n_heads, int n_kv, int hd, float scale, int window, int n_splits,
                                          int own_tiles, int hdv, float softcap, const float* sinks, int chunk,
                                          void* stream) {
+  return gi_attn_decode_generic_ex2(out, ldo, part_o, part_ml, q, ldq, dtype, kcache, vcache, block_table, max_pages, seq_slots,
+                                    seq_lens, n_seqs, n_heads, n_kv, hd, scale, window, n_splits, own_tiles, hdv, softcap, sinks,
+                                    chunk, hdv, stream);
+}
+
+extern "C" int gi_attn_decode_generic_ex2(void* out, long ldo, float* part_o, float* part_ml, const void* q, long ldq,
+                                          int dtype, const void* kcache, const void* vcache, const int* block_table,
+                                          int max_pages, const int* seq_slots, const int* seq_lens, int n_seqs,
+                                          int n_heads, int n_kv, int hd, float scale, int window, int n_splits,
+                                          int own_tiles, int hdv, float softcap, const float* sinks, int chunk,
+                                          long v_row_stride, void* stream) {
   if (n_seqs <= 0) return GI_OK;
-  if (hdv <= 0 || hdv > 256) return gi::fail(GI_ERR_UNSUPPORTED, "attention: value size %d is outside 1..256", hdv);
+  if (hdv <= 0 || hdv > 512) return gi::fail(GI_ERR_UNSUPPORTED, "attention: value size %d is outside 1..512", hdv);
+  if (v_row_stride < hdv) return gi::fail(GI_ERR_ARG, "attention: value rows %ld apart cannot hold %d values", v_row_stride, hdv);
   if (chunk < 0 || softcap < 0.f) return gi::fail(GI_ERR_ARG, "attention: a chunk or a cap cannot be negative");
   if (own_tiles < 0) return gi::fail(GI_ERR_ARG, "attention: tiles per slice cannot be negative");
   if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0)
     return gi::fail(GI_ERR_ARG, "attention: %d heads do not divide into %d kv heads", n_heads, n_kv);
-  if (hd <= 0 || hd > 256) return gi::fail(GI_ERR_UNSUPPORTED, "attention: head size %d is outside 1..256", hd);
+  if (hd <= 0 || hd > 640) return gi::fail(GI_ERR_UNSUPPORTED, "attention: head size %d is outside 1..640", hd);
   if (n_splits < 1) return gi::fail(GI_ERR_ARG, "attention: at least one slice");
   if (n_splits > 1 && (!part_o || !part_ml)) return gi::fail(GI_ERR_ARG, "attention: slices need scratch memory");
   const int group = n_heads / n_kv;
@@ -519,7 +546,7 @@ extern "C" int gi_attn_decode_generic_ex(void* out, long ldo, float* part_o, flo
     GI_DISPATCH_DTYPE(dtype, T,                                                                                    \
         rc = (launch_decode_dc<T, G>(dc, grid, smem, s, (T*)out, ldo, part_o, part_ml, (const T*)q, ldq, (const T*)kcache, \
                                      (const T*)vcache, block_table, max_pages, seq_slots, seq_lens, n_heads, n_kv, hd, \
-                                     scale, window, n_splits, own_tiles, hdv, softcap, sinks, chunk)));            \
+                                     scale, window, n_splits, own_tiles, hdv, softcap, sinks, chunk, v_row_stride))); \
     break;
   switch (gc) {
     GI_GC_CASE(1)

@@ -1,0 +1,370 @@
+// Row kernels and small products for layers whose attention keeps one low-rank latent per token instead of keys and
+// values per head, and for feed-forwards with biases and a squared relu.
+//
+//  * layernorm:        y = (x - mean) / sqrt(var + eps) * w, statistics in 32-bit, one block per row.
+//  * bias_act:         out = act(in + bias) over rows, and (optionally, in the same launch) residual rows += a bias.
+//  * latent_prepare:   one token's row [query latent | key/value latent | shared rotary key part] of the down product:
+//                      the query latent is RMS-normed for the next product; the key/value latent is RMS-normed and,
+//                      with the rotated key part behind it, written to the token's place in the paged cache.
+//  * latent_query_rot: the rotary part of every head's query, rotated, into the rows the attention reads
+//                      ([heads][latent | rotary part]); the latent part of those rows comes from bmm_heads.
+//  * bmm_heads:        out[t, h, :] = W_h a[t, h, :], one small matrix per head (the keys' up-projection folded onto the
+//                      queries, the values' up-projection applied to the attention's output).
+#include <math.h>
+
+#include "api.h"
+#include "common.cuh"
+#include "mma_utils.cuh"
+
+namespace {
+
+// ---- layer norm --------------------------------------------------------------------------------------------------
+// The order of every sum follows from the width alone (256 threads, a fixed tree), so a row gives the same bits in any step.
+template <typename TO, typename TW>
+__global__ void __launch_bounds__(256)
+layernorm_kernel(TO* __restrict__ out, const float* x, const TW* __restrict__ w, const int* rows, int d, float eps) {
+  __shared__ float scratch[33];
+  gi::pdl_prologue();
+  const int r = blockIdx.x;
+  const int m = rows ? rows[r] : r;
+  const float* xr = x + (size_t)m * d;
+  TO* o = out + (size_t)r * d;
+  constexpr int PER = 8;
+  const bool in_regs = d <= PER * 256;
+  float v[PER];
+  float s = 0.f;
+  if (in_regs) {
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      const int i = threadIdx.x + j * 256;
+      v[j] = i < d ? xr[i] : 0.f;
+      s += v[j];
+    }
+  } else {
+    for (int i = threadIdx.x; i < d; i += 256) s += xr[i];
+  }
+  const float mean = gi::block_sum(s, scratch) / (float)d;
+  float q = 0.f;
+  if (in_regs) {
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      const int i = threadIdx.x + j * 256;
+      const float dv = i < d ? v[j] - mean : 0.f;
+      q = fmaf(dv, dv, q);
+    }
+  } else {
+    for (int i = threadIdx.x; i < d; i += 256) {
+      const float dv = xr[i] - mean;
+      q = fmaf(dv, dv, q);
+    }
+  }
+  const float rstd = 1.0f / sqrtf(gi::block_sum(q, scratch) / (float)d + eps);
+  if (in_regs) {
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      const int i = threadIdx.x + j * 256;
+      if (i < d) gi::stf(o + i, (v[j] - mean) * rstd * gi::ldf(w + i));
+    }
+  } else {
+    for (int i = threadIdx.x; i < d; i += 256) gi::stf(o + i, (xr[i] - mean) * rstd * gi::ldf(w + i));
+  }
+}
+
+// ---- bias and activation -------------------------------------------------------------------------------------------
+// act 0: none; 1: relu(z)^2.
+template <typename T, typename TW>
+__global__ void bias_act_kernel(T* __restrict__ out, const T* in, long ld_in, const TW* __restrict__ bias, int f, size_t total_act,
+                                int act, float* residual, const TW* __restrict__ res_bias, int d, size_t total) {
+  gi::pdl_prologue();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  if (i < total_act) {
+    const size_t m = i / f, c = i % f;
+    float z = gi::ldf(in + m * ld_in + c);
+    if (bias != nullptr) z += gi::ldf(bias + c);
+    if (act == 1) {
+      z = fmaxf(z, 0.f);
+      z *= z;
+    }
+    gi::stf(out + i, z);
+  } else {
+    const size_t k = i - total_act;
+    residual[k] += gi::ldf(res_bias + k % d);
+  }
+}
+
+// ---- the latent's row --------------------------------------------------------------------------------------------
+template <typename T, typename TW>
+__global__ void __launch_bounds__(128)
+latent_prepare_kernel(T* __restrict__ cq, const T* in, long ld, const TW* __restrict__ wq, const TW* __restrict__ wc, float eps,
+                      const float2* table, int half, const int* positions, const int* slots, const int* block_table,
+                      int max_pages, T* kcache, int rq, int r, int dr, int write_cache) {
+  __shared__ float scratch[33];
+  gi::pdl_prologue();
+  const int t = blockIdx.x;
+  const T* row = in + (size_t)t * ld;
+  // the queries' latent: x / sqrt(mean(x^2) + eps) * w
+  if (rq > 0) {
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < rq; i += 128) {
+      const float v = gi::ldf(row + i);
+      ss = fmaf(v, v, ss);
+    }
+    const float rs = 1.0f / sqrtf(gi::block_sum(ss, scratch) / (float)rq + eps);
+    for (int i = threadIdx.x; i < rq; i += 128) gi::stf(cq + (size_t)t * rq + i, gi::ldf(row + i) * rs * gi::ldf(wq + i));
+  }
+  if (!write_cache) return;
+  const int slot = slots[t];
+  const int pos = max(positions[t], 0);
+  const int page = slot >= 0 ? block_table[(size_t)slot * max_pages + pos / PAGE_TOKENS] : 0;
+  T* dst = kcache + ((size_t)page * PAGE_TOKENS + pos % PAGE_TOKENS) * (size_t)(r + dr);
+  const T* lat = row + rq;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < r; i += 128) {
+    const float v = gi::ldf(lat + i);
+    ss = fmaf(v, v, ss);
+  }
+  const float rs = 1.0f / sqrtf(gi::block_sum(ss, scratch) / (float)r + eps);
+  for (int i = threadIdx.x; i < r; i += 128) gi::stf(dst + i, gi::ldf(lat + i) * rs * gi::ldf(wc + i));
+  // the key part all heads share: its first 2 * half numbers turn in neighbouring pairs, the rest pass
+  const T* kr = lat + r;
+  for (int i = threadIdx.x; i < half; i += 128) {
+    float a, b;
+    gi::rotate_pair(gi::ldf(kr + 2 * i), gi::ldf(kr + 2 * i + 1), table[(size_t)t * half + i], &a, &b);
+    gi::stf(dst + r + 2 * i, a);
+    gi::stf(dst + r + 2 * i + 1, b);
+  }
+  for (int i = 2 * half + threadIdx.x; i < dr; i += 128) dst[r + i] = kr[i];
+}
+
+template <typename T>
+__global__ void latent_query_rot_kernel(T* qa, long ldqa, const T* q, long ldq, const float2* table, int half, int dn, int dr,
+                                        int r) {
+  gi::pdl_prologue();
+  const int t = blockIdx.x, h = blockIdx.y;
+  const T* src = q + (size_t)t * ldq + (size_t)h * (dn + dr) + dn;
+  T* dst = qa + (size_t)t * ldqa + (size_t)h * (r + dr) + r;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    float a, b;
+    gi::rotate_pair(gi::ldf(src + 2 * i), gi::ldf(src + 2 * i + 1), table[(size_t)t * half + i], &a, &b);
+    gi::stf(dst + 2 * i, a);
+    gi::stf(dst + 2 * i + 1, b);
+  }
+  for (int i = 2 * half + threadIdx.x; i < dr; i += blockDim.x) dst[i] = src[i];
+}
+
+// ---- one small product per head, CUDA cores ------------------------------------------------------------------------
+// out[t, h * ohs + n] = sum_k a[t, h * ahs + k] * W[h * whs + n * ldw + k * kstride]; every output is summed by one thread
+// in k order, so a row's result does not depend on the step's other rows.
+constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
+
+template <typename TA, typename TW, typename TO>
+__global__ void __launch_bounds__(256)
+bmm_heads_kernel(TO* __restrict__ out, long ldo, long ohs, const TA* A, long lda, long ahs, const TW* __restrict__ W, long whs,
+                 long ldw, long kstride, int M, int N, int K) {
+  __shared__ float As[BK][BM + 4];
+  __shared__ float Ws[BK][BN + 4];
+  gi::pdl_prologue();
+  const int h = blockIdx.z, m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const TA* Ah = A + (size_t)h * ahs;
+  const TW* Wh = W + (size_t)h * whs;
+  const int tid = threadIdx.x, tx = tid % 16, ty = tid / 16;
+  float acc[TM][TN];
+#pragma unroll
+  for (int i = 0; i < TM; ++i)
+#pragma unroll
+    for (int j = 0; j < TN; ++j) acc[i][j] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += BK) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int idx = tid + q * 256;
+      const int rr = idx / BK, kk = idx % BK, k = k0 + kk;
+      float a = 0.f, w = 0.f;
+      if (k < K) {
+        if (m0 + rr < M) a = gi::ldf(Ah + (size_t)(m0 + rr) * lda + k);
+        if (n0 + rr < N) w = gi::ldf(Wh + (size_t)(n0 + rr) * ldw + (size_t)k * kstride);
+      }
+      As[kk][rr] = a;
+      Ws[kk][rr] = w;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < BK; ++kk) {
+      float a[TM], w[TN];
+#pragma unroll
+      for (int i = 0; i < TM; ++i) a[i] = As[kk][ty * TM + i];
+#pragma unroll
+      for (int j = 0; j < TN; ++j) w[j] = Ws[kk][tx * TN + j];
+#pragma unroll
+      for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < TM; ++i) {
+    const int m = m0 + ty * TM + i;
+    if (m >= M) continue;
+#pragma unroll
+    for (int j = 0; j < TN; ++j) {
+      const int n = n0 + tx * TN + j;
+      if (n < N) gi::stf(out + (size_t)m * ldo + (size_t)h * ohs + n, acc[i][j]);
+    }
+  }
+}
+
+// ---- the same on tensor cores: bfloat16 in and out, W_h stored [N][K] row-major (kstride 1) -------------------------------
+// A block takes 64 rows x 64 columns of one head: four warps of 16 rows each, `mma.sync m16n8k16` with 32-bit sums; the
+// operands of a 32-wide slice of K go through shared memory (rows padded to 40 values, so that the fragments' loads
+// meet no bank twice).  Edges are filled with zeros and not stored.
+constexpr int TK = 32, TLD = TK + 8;
+
+__global__ void __launch_bounds__(128)
+bmm_heads_mma_kernel(__nv_bfloat16* __restrict__ out, long ldo, long ohs, const __nv_bfloat16* A, long lda, long ahs,
+                     const __nv_bfloat16* __restrict__ W, long whs, long ldw, int M, int N, int K) {
+  __shared__ __align__(16) __nv_bfloat16 As[64 * TLD];
+  __shared__ __align__(16) __nv_bfloat16 Ws[64 * TLD];
+  gi::pdl_prologue();
+  const int h = blockIdx.z, m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+  const __nv_bfloat16* Ah = A + (size_t)h * ahs;
+  const __nv_bfloat16* Wh = W + (size_t)h * whs;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
+  float acc[8][4];
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
+  const __nv_bfloat16 zero = __float2bfloat16_rn(0.f);
+  for (int k0 = 0; k0 < K; k0 += TK) {
+    // 64 rows x 32 values of each operand: 2048 values, 16 per thread, in pairs
+    for (int idx = tid; idx < 64 * (TK / 2); idx += 128) {
+      const int rr = idx / (TK / 2), kk = 2 * (idx % (TK / 2)), k = k0 + kk;
+      __nv_bfloat16 a0 = zero, a1 = zero, w0 = zero, w1 = zero;
+      if (m0 + rr < M) {
+        const __nv_bfloat16* p = Ah + (size_t)(m0 + rr) * lda + k;
+        if (k < K) a0 = p[0];
+        if (k + 1 < K) a1 = p[1];
+      }
+      if (n0 + rr < N) {
+        const __nv_bfloat16* p = Wh + (size_t)(n0 + rr) * ldw + k;
+        if (k < K) w0 = p[0];
+        if (k + 1 < K) w1 = p[1];
+      }
+      As[rr * TLD + kk] = a0;
+      As[rr * TLD + kk + 1] = a1;
+      Ws[rr * TLD + kk] = w0;
+      Ws[rr * TLD + kk + 1] = w1;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int ks = 0; ks < TK; ks += 16) {
+      uint32_t a[4];
+      const __nv_bfloat16* ar = As + (warp * 16 + g) * TLD + ks + 2 * c;
+      a[0] = *reinterpret_cast<const uint32_t*>(ar);
+      a[1] = *reinterpret_cast<const uint32_t*>(ar + 8 * TLD);
+      a[2] = *reinterpret_cast<const uint32_t*>(ar + 8);
+      a[3] = *reinterpret_cast<const uint32_t*>(ar + 8 * TLD + 8);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const __nv_bfloat16* wr = Ws + (j * 8 + g) * TLD + ks + 2 * c;
+        uint32_t b[2];
+        b[0] = *reinterpret_cast<const uint32_t*>(wr);
+        b[1] = *reinterpret_cast<const uint32_t*>(wr + 8);
+        gi::mma_16816(acc[j], a, b[0], b[1]);
+      }
+    }
+    __syncthreads();
+  }
+  const int r_lo = m0 + warp * 16 + g, r_hi = r_lo + 8;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int n = n0 + j * 8 + 2 * c;
+    if (n < N) {
+      if (r_lo < M) out[(size_t)r_lo * ldo + (size_t)h * ohs + n] = __float2bfloat16_rn(acc[j][0]);
+      if (r_hi < M) out[(size_t)r_hi * ldo + (size_t)h * ohs + n] = __float2bfloat16_rn(acc[j][2]);
+    }
+    if (n + 1 < N) {
+      if (r_lo < M) out[(size_t)r_lo * ldo + (size_t)h * ohs + n + 1] = __float2bfloat16_rn(acc[j][1]);
+      if (r_hi < M) out[(size_t)r_hi * ldo + (size_t)h * ohs + n + 1] = __float2bfloat16_rn(acc[j][3]);
+    }
+  }
+}
+
+}  // namespace
+
+extern "C" int gi_layernorm(void* out, int out_dtype, const float* x, const void* w, int w_dtype, const int* rows, int n_rows,
+                            int d, float eps, void* stream) {
+  if (n_rows <= 0) return GI_OK;
+  if (d <= 0) return gi::fail(GI_ERR_ARG, "layernorm: bad width %d", d);
+  cudaError_t e = cudaSuccess;
+  GI_DISPATCH_DTYPE(out_dtype, TO, GI_DISPATCH_DTYPE(w_dtype, TW,
+      e = gi::launch(layernorm_kernel<TO, TW>, dim3(n_rows), dim3(256), 0, (cudaStream_t)stream, (TO*)out, x, (const TW*)w, rows, d, eps)));
+  return gi::check(e, "layernorm");
+}
+
+extern "C" int gi_bias_act(void* out, const void* in, int dtype, long ld_in, const void* bias, int w_dtype, int n_rows, int f,
+                           int act, float* residual, const void* res_bias, int d, void* stream) {
+  if (n_rows <= 0) return GI_OK;
+  if (f <= 0 || (act != 0 && act != 1)) return gi::fail(GI_ERR_ARG, "bias_act: bad width %d or activation %d", f, act);
+  if ((residual != nullptr) != (res_bias != nullptr) || (residual != nullptr && d <= 0))
+    return gi::fail(GI_ERR_ARG, "bias_act: a bias for the residual rows needs both the rows and the bias");
+  const size_t total_act = (size_t)n_rows * f;
+  const size_t total = total_act + (residual != nullptr ? (size_t)n_rows * d : 0);
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  cudaError_t e = cudaSuccess;
+  GI_DISPATCH_DTYPE(dtype, T, GI_DISPATCH_DTYPE(w_dtype, TW,
+      e = gi::launch(bias_act_kernel<T, TW>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, (T*)out, (const T*)in, ld_in,
+                     (const TW*)bias, f, total_act, act, residual, (const TW*)res_bias, d, total)));
+  return gi::check(e, "bias_act");
+}
+
+extern "C" int gi_latent_prepare(void* cq, const void* in, int dtype, long ld, const void* wq, const void* wc, int w_dtype,
+                                 float eps, const float* table, int rot, const int* positions, const int* slots,
+                                 const int* block_table, int max_pages, void* kcache, int n_tokens, int rq, int r, int dr,
+                                 int write_cache, void* stream) {
+  if (n_tokens <= 0) return GI_OK;
+  if (rq < 0 || r <= 0 || dr < 0 || rot < 0 || rot % 2 != 0 || rot > dr)
+    return gi::fail(GI_ERR_ARG, "latent rows: bad sizes (query latent %d, latent %d, rotary part %d of which %d turn)", rq, r, dr, rot);
+  if (rot > 0 && table == nullptr) return gi::fail(GI_ERR_ARG, "latent rows: no table of angles");
+  if (write_cache && (!kcache || !block_table || !slots || !positions)) return gi::fail(GI_ERR_ARG, "latent rows: cache write without a cache");
+  cudaError_t e = cudaSuccess;
+  GI_DISPATCH_DTYPE(dtype, T, GI_DISPATCH_DTYPE(w_dtype, TW,
+      e = gi::launch(latent_prepare_kernel<T, TW>, dim3(n_tokens), dim3(128), 0, (cudaStream_t)stream, (T*)cq, (const T*)in, ld,
+                     (const TW*)wq, (const TW*)wc, eps, (const float2*)table, rot / 2, positions, slots, block_table, max_pages,
+                     (T*)kcache, rq, r, dr, write_cache)));
+  return gi::check(e, "latent rows");
+}
+
+extern "C" int gi_latent_query_rot(void* qa, long ldqa, const void* q, long ldq, int dtype, const float* table, int rot,
+                                   int n_tokens, int n_heads, int dn, int dr, int r, void* stream) {
+  if (n_tokens <= 0 || dr <= 0) return GI_OK;
+  if (rot < 0 || rot % 2 != 0 || rot > dr || n_heads <= 0 || n_heads > 65535)
+    return gi::fail(GI_ERR_ARG, "latent queries: bad sizes (%d heads, rotary part %d of which %d turn)", n_heads, dr, rot);
+  if (rot > 0 && table == nullptr) return gi::fail(GI_ERR_ARG, "latent queries: no table of angles");
+  cudaError_t e = cudaSuccess;
+  GI_DISPATCH_DTYPE(dtype, T,
+      e = gi::launch(latent_query_rot_kernel<T>, dim3(n_tokens, n_heads), dim3(32), 0, (cudaStream_t)stream, (T*)qa, ldqa,
+                     (const T*)q, ldq, (const float2*)table, rot / 2, dn, dr, r));
+  return gi::check(e, "latent queries");
+}
+
+extern "C" int gi_bmm_heads(void* out, long ldo, long ohs, const void* a, long lda, long ahs, int dtype, const void* w, int w_dtype,
+                            long whs, long ldw, long kstride, int M, int N, int K, int heads, int tensor_cores, void* stream) {
+  if (M <= 0 || heads <= 0) return GI_OK;
+  if (N <= 0 || K <= 0) return gi::fail(GI_ERR_ARG, "per-head product: bad sizes N=%d K=%d", N, K);
+  const long my = (M + 63) / 64;
+  if (heads > 65535 || my > 65535) return gi::fail(GI_ERR_UNSUPPORTED, "per-head product: more than 65535 heads or row tiles");
+  dim3 grid((N + 63) / 64, (unsigned)my, heads);
+  cudaError_t e = cudaSuccess;
+  if (tensor_cores && dtype == GI_BF16 && w_dtype == GI_BF16 && kstride == 1 && lda % 2 == 0 && ahs % 2 == 0 && ldw % 2 == 0 &&
+      whs % 2 == 0 && !(((uintptr_t)a | (uintptr_t)w) & 3)) {
+    e = gi::launch(bmm_heads_mma_kernel, grid, dim3(128), 0, (cudaStream_t)stream, (__nv_bfloat16*)out, ldo, ohs,
+                   (const __nv_bfloat16*)a, lda, ahs, (const __nv_bfloat16*)w, whs, ldw, M, N, K);
+    return gi::check(e, "per-head product");
+  }
+  GI_DISPATCH_DTYPE(dtype, T, GI_DISPATCH_DTYPE(w_dtype, TW,
+      e = gi::launch(bmm_heads_kernel<T, TW, T>, grid, dim3(256), 0, (cudaStream_t)stream, (T*)out, ldo, ohs, (const T*)a, lda, ahs,
+                     (const TW*)w, whs, ldw, kstride, M, N, K)));
+  return gi::check(e, "per-head product");
+}

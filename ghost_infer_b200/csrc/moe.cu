@@ -49,7 +49,7 @@ template <typename T, typename TW>
 __global__ void __launch_bounds__(128)
 route_kernel(int* __restrict__ ids, float* __restrict__ wts, float* __restrict__ sgate, const T* __restrict__ h, long ldh,
              const TW* __restrict__ w_router, const TW* __restrict__ w_sg, int n_tokens, int width, int experts, int top,
-             int vec) {
+             int vec, int score_mode) {
   extern __shared__ __align__(16) float sm[];
   float* hs = sm;                          // [width] (rounded up to a multiple of 8)
   float* lg = sm + ((width + 7) / 8) * 8;  // [experts]
@@ -98,7 +98,8 @@ route_kernel(int* __restrict__ ids, float* __restrict__ wts, float* __restrict__
     }
     if (at == 0x7fffffff) at = k < experts ? k : 0;      // every logit a NaN: any expert, never an index outside
     if (k == 0) first = best;
-    const float ex = expf(best - first);
+    // score_mode 0: the weights are the softmax over the chosen logits; 1: each chosen logit's own sigmoid, as it is
+    const float ex = score_mode == 1 ? 1.0f / (1.0f + expf(-best)) : expf(best - first);
     sum += ex;
     if (lane == k) mine = ex;
     if (lane == 0) {
@@ -107,7 +108,7 @@ route_kernel(int* __restrict__ ids, float* __restrict__ wts, float* __restrict__
     }
     __syncwarp();
   }
-  if (lane < top) wts[(size_t)t * top + lane] = mine / sum;
+  if (lane < top) wts[(size_t)t * top + lane] = score_mode == 1 ? mine : mine / sum;
 }
 
 // ---- plan ------------------------------------------------------------------------------------------------------
@@ -194,7 +195,7 @@ template <typename TA, typename TW, bool DUAL>
 __global__ void __launch_bounds__(256)
 expert_gemm_kernel(void* __restrict__ out_, const TA* __restrict__ A, long lda, const TW* __restrict__ W, long w_stride,
                    const int* __restrict__ offsets, const int* __restrict__ perm, int top, int experts, int N, int K,
-                   int interleaved) {
+                   int interleaved, int act_out) {
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
   __shared__ float Us[DUAL ? BK : 1][BN + 4];
@@ -268,6 +269,9 @@ expert_gemm_kernel(void* __restrict__ out_, const TA* __restrict__ A, long lda, 
       if (DUAL) {
         const float g = acc[i][j];
         gi::stf((TA*)out_ + (size_t)r * N + n, g / (1.0f + expf(-g)) * acu[i][j]);
+      } else if (act_out) {          // a plain (ungated) hidden layer: relu squared, in the rows' type
+        const float z = fmaxf(acc[i][j], 0.f);
+        gi::stf((TA*)out_ + (size_t)r * N + n, z * z);
       } else {
         ((float*)out_)[(size_t)r * N + n] = acc[i][j];
       }
@@ -292,7 +296,8 @@ inline bool gemv_ok(int dtype, int w_dtype, int k, const void* a, const void* w,
 template <typename T, bool DUAL>
 __global__ void __launch_bounds__(GEMV_WARPS * 32)
 expert_gemv_kernel(void* __restrict__ out_, const T* __restrict__ A, long lda, const T* __restrict__ W, long w_stride,
-                   const int* __restrict__ offsets, const int* __restrict__ perm, int top, int N, int K, int interleaved) {
+                   const int* __restrict__ offsets, const int* __restrict__ perm, int top, int N, int K, int interleaved,
+                   int act_out) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   T* As = reinterpret_cast<T*>(smem_raw);            // [GEMV_ROWS][K]
   constexpr int VN = Vec16<T>::N;
@@ -364,7 +369,12 @@ expert_gemv_kernel(void* __restrict__ out_, const T* __restrict__ A, long lda, c
             const float u = gi::warp_sum(acu[jj][r]);
             if (lane == 0 && n < N) gi::stf((T*)out_ + (size_t)(r0 + r) * N + n, g / (1.0f + expf(-g)) * u);
           } else if (lane == 0 && n < N) {
-            ((float*)out_)[(size_t)(r0 + r) * N + n] = g;
+            if (act_out) {
+              const float z = fmaxf(g, 0.f);
+              gi::stf((T*)out_ + (size_t)(r0 + r) * N + n, z * z);
+            } else {
+              ((float*)out_)[(size_t)(r0 + r) * N + n] = g;
+            }
           }
         }
       }
@@ -376,11 +386,17 @@ expert_gemv_kernel(void* __restrict__ out_, const T* __restrict__ A, long lda, c
 // side by side.
 template <typename T>
 __global__ void gather_rows_kernel(T* __restrict__ out, const T* __restrict__ in, long ld_in, const int* __restrict__ idx,
-                                   int top, int width) {
+                                   int top, int width, const float* __restrict__ scale) {
   gi::pdl_prologue();
   const int r = blockIdx.x;
   const T* src = in + (size_t)(idx[r] / top) * ld_in;
-  for (int i = threadIdx.x; i < width; i += blockDim.x) out[(size_t)r * width + i] = src[i];
+  if (scale == nullptr) {
+    for (int i = threadIdx.x; i < width; i += blockDim.x) out[(size_t)r * width + i] = src[i];
+  } else {
+    // the entry's weight goes onto what the expert reads (32-bit product, rounded to the rows' type)
+    const float s = scale[idx[r]];
+    for (int i = threadIdx.x; i < width; i += blockDim.x) gi::stf(out + (size_t)r * width + i, gi::ldf(src + i) * s);
+  }
 }
 
 __global__ void __launch_bounds__(256)
@@ -391,8 +407,8 @@ combine_kernel(float* __restrict__ residual, const float* __restrict__ down, con
   const int t = blockIdx.x;
   for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < width; i += gridDim.y * blockDim.x) {
     float acc = 0.f;
-    for (int k = 0; k < top; ++k)
-      acc = fmaf(wts[(size_t)t * top + k], down[(size_t)inv[(size_t)t * top + k] * width + i], acc);
+    for (int k = 0; k < top; ++k)      // without weights (they went onto the experts' inputs): the plain sum
+      acc = fmaf(wts != nullptr ? wts[(size_t)t * top + k] : 1.0f, down[(size_t)inv[(size_t)t * top + k] * width + i], acc);
     if (shared != nullptr) acc = fmaf(sgate[t], shared[(size_t)t * width + i], acc);
     residual[(size_t)t * width + i] += acc;
   }
@@ -402,7 +418,14 @@ combine_kernel(float* __restrict__ residual, const float* __restrict__ down, con
 
 extern "C" int gi_moe_route(int* ids, float* wts, float* sgate, const void* h, int dtype, long ldh, const void* w_router,
                             const void* w_sg, int w_dtype, int n_tokens, int width, int experts, int top, void* stream) {
+  return gi_moe_route_scored(ids, wts, sgate, h, dtype, ldh, w_router, w_sg, w_dtype, n_tokens, width, experts, top, 0, stream);
+}
+
+extern "C" int gi_moe_route_scored(int* ids, float* wts, float* sgate, const void* h, int dtype, long ldh, const void* w_router,
+                                   const void* w_sg, int w_dtype, int n_tokens, int width, int experts, int top, int score_mode,
+                                   void* stream) {
   if (n_tokens <= 0) return GI_OK;
+  if (score_mode != 0 && score_mode != 1) return gi::fail(GI_ERR_ARG, "router: unknown kind of weights %d", score_mode);
   if (experts < 1 || top < 1 || top > experts || top > 32 || experts > 8192)
     return gi::fail(GI_ERR_UNSUPPORTED, "router: %d of %d experts (at most 32 of 8192)", top, experts);
   if (w_sg != nullptr && sgate == nullptr) return gi::fail(GI_ERR_ARG, "router: a shared gate needs somewhere to go");
@@ -416,7 +439,7 @@ extern "C" int gi_moe_route(int* ids, float* wts, float* sgate, const void* h, i
       if (smem > 48 * 1024) e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e == cudaSuccess)
         e = gi::launch(kern, dim3(n_tokens), dim3(128), smem, (cudaStream_t)stream, ids, wts, sgate, (const T*)h, ldh,
-                       (const TW*)w_router, (const TW*)w_sg, n_tokens, width, experts, top, vec);
+                       (const TW*)w_router, (const TW*)w_sg, n_tokens, width, experts, top, vec, score_mode);
   }));
   return gi::check(e, "router");
 }
@@ -455,7 +478,7 @@ extern "C" int gi_moe_gemm_gate_up(void* out, int dtype, const void* a, long lda
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e == cudaSuccess)
           e = gi::launch(kern, grid, dim3(GEMV_WARPS * 32), smem, (cudaStream_t)stream, out, (const T*)a, lda, (const T*)w, w_stride,
-                         offsets, perm, top, f, k, interleaved);
+                         offsets, perm, top, f, k, interleaved, 0);
     });
     return gi::check(e, "expert product (gate, up; few rows)");
   }
@@ -465,13 +488,19 @@ extern "C" int gi_moe_gemm_gate_up(void* out, int dtype, const void* a, long lda
   cudaError_t e = cudaSuccess;
   GI_DISPATCH_DTYPE(dtype, TA, GI_DISPATCH_DTYPE(w_dtype, TW,
       e = gi::launch(expert_gemm_kernel<TA, TW, true>, grid, dim3(256), 0, (cudaStream_t)stream, out, (const TA*)a, lda,
-                     (const TW*)w, w_stride, offsets, perm, top, experts, f, k, interleaved)));
+                     (const TW*)w, w_stride, offsets, perm, top, experts, f, k, interleaved, 0)));
   return gi::check(e, "expert product (gate, up)");
 }
 
 extern "C" int gi_moe_gemm_down(float* out, const void* a, int dtype, long lda, const void* w, int w_dtype, long w_stride,
                                 const int* offsets, int entries, int experts, int n, int k, void* stream) {
+  return gi_moe_gemm_rows((void*)out, a, dtype, lda, w, w_dtype, w_stride, offsets, entries, experts, n, k, 0, stream);
+}
+
+extern "C" int gi_moe_gemm_rows(void* out, const void* a, int dtype, long lda, const void* w, int w_dtype, long w_stride,
+                                const int* offsets, int entries, int experts, int n, int k, int act_out, void* stream) {
   if (entries <= 0) return GI_OK;
+  if (act_out != 0 && act_out != 1) return gi::fail(GI_ERR_ARG, "expert product: unknown activation %d", act_out);
   if (n <= 0 || k <= 0) return gi::fail(GI_ERR_ARG, "expert product: bad sizes");
   if (entries <= GEMV_MAX_ENTRIES && gemv_ok(dtype, w_dtype, k, a, w, lda)) {
     cudaError_t e = cudaSuccess;
@@ -482,7 +511,7 @@ extern "C" int gi_moe_gemm_down(float* out, const void* a, int dtype, long lda, 
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e == cudaSuccess)
           e = gi::launch(kern, grid, dim3(GEMV_WARPS * 32), smem, (cudaStream_t)stream, (void*)out, (const T*)a, lda, (const T*)w,
-                         w_stride, offsets, (const int*)nullptr, 1, n, k, 0);
+                         w_stride, offsets, (const int*)nullptr, 1, n, k, 0, act_out);
     });
     return gi::check(e, "expert product (down; few rows)");
   }
@@ -492,7 +521,7 @@ extern "C" int gi_moe_gemm_down(float* out, const void* a, int dtype, long lda, 
   cudaError_t e = cudaSuccess;
   GI_DISPATCH_DTYPE(dtype, TA, GI_DISPATCH_DTYPE(w_dtype, TW,
       e = gi::launch(expert_gemm_kernel<TA, TW, false>, grid, dim3(256), 0, (cudaStream_t)stream, (void*)out, (const TA*)a, lda,
-                     (const TW*)w, w_stride, offsets, (const int*)nullptr, 1, experts, n, k, 0)));
+                     (const TW*)w, w_stride, offsets, (const int*)nullptr, 1, experts, n, k, 0, act_out)));
   return gi::check(e, "expert product (down)");
 }
 
@@ -508,11 +537,16 @@ extern "C" int gi_moe_combine(float* residual, const float* down, const int* inv
 
 extern "C" int gi_moe_gather_rows(void* out, const void* in, int dtype, long ld_in, const int* perm, int entries, int top,
                                   int width, void* stream) {
+  return gi_moe_gather_rows_scaled(out, in, dtype, ld_in, perm, nullptr, entries, top, width, stream);
+}
+
+extern "C" int gi_moe_gather_rows_scaled(void* out, const void* in, int dtype, long ld_in, const int* perm, const float* scale,
+                                         int entries, int top, int width, void* stream) {
   if (entries <= 0) return GI_OK;
   if (top < 1 || width <= 0) return gi::fail(GI_ERR_ARG, "gather: bad sizes");
   cudaError_t e = cudaSuccess;
   GI_DISPATCH_DTYPE(dtype, T, e = gi::launch(gather_rows_kernel<T>, dim3(entries), dim3(256), 0, (cudaStream_t)stream, (T*)out,
-                                             (const T*)in, ld_in, perm, top, width));
+                                             (const T*)in, ld_in, perm, top, width, scale));
   return gi::check(e, "gather rows");
 }
 

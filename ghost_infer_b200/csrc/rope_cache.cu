@@ -14,14 +14,14 @@ namespace {
 // (cos, sin) of pos * inv_freq for every token of a step and every rotated pair: computed once per step and
 // shared by all layers, which rotate with the same positions and frequencies.
 __global__ void rope_table_kernel(float2* __restrict__ table, const int* __restrict__ positions,
-                                  const float* __restrict__ inv_freq, int half, int total) {
+                                  const float* __restrict__ inv_freq, int half, int total, float magnitude) {
   gi::pdl_prologue();
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const int t = idx / half, i = idx % half;
   float s, c;
   sincosf((float)positions[t] * inv_freq[i], &s, &c);
-  table[idx] = make_float2(c, s);
+  table[idx] = magnitude == 1.0f ? make_float2(c, s) : make_float2(c * magnitude, s * magnitude);
 }
 
 using gi::rotate_pair;
@@ -161,10 +161,15 @@ __global__ void rope_cache_rows_kernel(T* __restrict__ qkv, long ld, const float
 }  // namespace
 
 extern "C" int gi_rope_table(float* table, const int* positions, const float* inv_freq, int n_tokens, int rot, void* stream) {
+  return gi_rope_table_scaled(table, positions, inv_freq, n_tokens, rot, 1.0f, stream);
+}
+
+extern "C" int gi_rope_table_scaled(float* table, const int* positions, const float* inv_freq, int n_tokens, int rot,
+                                    float magnitude, void* stream) {
   const int half = rot / 2, total = n_tokens * half;
   if (total <= 0) return GI_OK;
   return gi::check(gi::launch(rope_table_kernel, dim3((total + 255) / 256), dim3(256), 0, (cudaStream_t)stream, (float2*)table,
-                              positions, inv_freq, half, total), "rope table");
+                              positions, inv_freq, half, total, magnitude), "rope table");
 }
 
 namespace {

@@ -69,6 +69,8 @@ class Model:
         self.spec = spec
         self.config = config
         self.embedding = lookup("embedding", spec.embedding.kind)(spec.embedding.params, spec.embedding_prefix)
+        en = getattr(spec, "embedding_norm", None)
+        self.embedding_norm = None if en is None else lookup("norm", en.kind)(en.params, spec.embedding_norm_prefix)
         self.layers = [Layer(ls, i) for i, ls in enumerate(spec.layers)]
         self.final_norm = lookup("norm", spec.final_norm.kind)(spec.final_norm.params, spec.final_norm_prefix)
         self.head = lookup("head", spec.head.kind)(spec.head.params, spec.head_prefix)
@@ -77,6 +79,8 @@ class Model:
     # ---- weights ------------------------------------------------------------------------------
     def weight_manifest(self) -> List[WeightSpec]:
         out = list(self.embedding.weights())
+        if self.embedding_norm is not None:
+            out.extend(self.embedding_norm.weights())
         for layer in self.layers:
             out.extend(layer.weights())
         out.extend(self.final_norm.weights())
@@ -95,6 +99,8 @@ class Model:
     def bind(self, tensors: Mapping[str, torch.Tensor], dtype, device="cuda") -> "Model":
         self.rt = Runtime(torch.device(device), _dtype_of(dtype))
         self.embedding.bind(tensors, self.rt)
+        if self.embedding_norm is not None:
+            self.embedding_norm.bind(tensors, self.rt)
         for layer in self.layers:
             layer.bind(tensors, self.rt)
         self.final_norm.bind(tensors, self.rt)

@@ -136,7 +136,7 @@ class Engine:
             m = layers[e.layer].block.mixer
             if m is not None and all(m is not seen for seen in self._mixers):
                 self._mixers.append(m)
-        parts = [getattr(model, n, None) for n in ("embedding", "final_norm", "head")] + [p for layer in layers for p in layer.block.parts()]
+        parts = [getattr(model, n, None) for n in ("embedding", "embedding_norm", "final_norm", "head")] + [p for layer in layers for p in layer.block.parts()]
         self.plans_on_host = any(getattr(p, "plans_on_host", False) for p in parts)
 
     # ---- host-side checks, before anything is launched (src/model.rs:974-982) -------------------
@@ -219,7 +219,10 @@ class Engine:
         from ..kernels import ops
         model = self.model
         # the residual stream: a tensor that a deferred product may leave partial sums for (they travel with it)
-        x = ops.as_carrier(model.embedding.forward(ctx.tokens))
+        x = model.embedding.forward(ctx.tokens)
+        if getattr(model, "embedding_norm", None) is not None:      # the stream stays 32-bit
+            x = model.embedding_norm.forward(x, out_dtype=torch.float32)
+        x = ops.as_carrier(x)
         for i, e in enumerate(model.spec.schedule):
             model.layers[e.layer].block.forward(x, ctx, self.cache.memory(i))
         if ctx.logit_rows is None:

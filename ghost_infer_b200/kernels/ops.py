@@ -87,6 +87,17 @@ def _bind():
         "gi_moe_experts_tc": [P, P, P, P, L, P, L, P, I, I, I, P, P, I, P],
         "gi_moe_gemm_down": [P, P, I, L, P, I, L, P, I, I, I, I, P],
         "gi_moe_combine": [P, P, P, P, P, P, I, I, I, P],
+        "gi_moe_route_scored": [P, P, P, P, I, L, P, P, I, I, I, I, I, I, P],
+        "gi_moe_gemm_rows": [P, P, I, L, P, I, L, P, I, I, I, I, I, P],
+        "gi_moe_gather_rows_scaled": [P, P, I, L, P, P, I, I, I, P],
+        "gi_attn_prefill_generic_ex2": [P, L, P, L, I, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, F, P, I, L, P],
+        "gi_attn_decode_generic_ex2": [P, L, P, P, P, L, I, P, P, P, I, P, P, I, I, I, I, F, I, I, I, I, F, P, I, L, P],
+        "gi_layernorm": [P, I, P, P, I, P, I, I, F, P],
+        "gi_bias_act": [P, P, I, L, P, I, I, I, I, P, P, I, P],
+        "gi_latent_prepare": [P, P, I, L, P, P, I, F, P, I, P, P, P, I, P, I, I, I, I, I, P],
+        "gi_latent_query_rot": [P, L, P, L, I, P, I, I, I, I, I, I, P],
+        "gi_bmm_heads": [P, L, L, P, L, L, I, P, I, L, L, L, I, I, I, I, I, P],
+        "gi_rope_table_scaled": [P, P, P, I, I, F, P],
     }
     for name, argtypes in sigs.items():
         fn = getattr(lib, name)
@@ -491,7 +502,7 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, mode: int, out: Optional[torch
 TUNE = {"small_skinny": False, "attn_waves": 1.0, "attn_tile_keys": 16, "defer_residual": True, "attn_prefill_tcgen05": True, "prefetch_units": 16,
         "attn_merge_inside": False, "attn_own_slices": False, "attn_stages_hd64": 2, "attn_stages_hd128": 3, "attn_rope_inside": False, "stream_whole_percent": 80,
         "attn_keys_on_rows": True, "attn_kr_warps": 6, "attn_kr_stages": 2, "qkv_rope_epilogue": True, "attn_min_slice": 256,
-        "attn_general_tc": True}
+        "attn_general_tc": True, "bmm_heads_tc": True, "attn_latent_tc": True}
 USE_STREAM = True    # decode products through the persistent stream-K kernel (else the mma.sync kernel)
 
 
@@ -765,15 +776,16 @@ def _tc_out_ok(out: Optional[torch.Tensor], mode: int, cols: int) -> bool:
     return out.stride(1) == 1 and out.stride(0) % align == 0 and out.data_ptr() % 16 == 0
 
 
-def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
-    """float32 [tokens, pairs, 2]: (cos, sin) of position * frequency, angles formed in 32-bit."""
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, magnitude: float = 1.0) -> torch.Tensor:
+    """float32 [tokens, pairs, 2]: (cos, sin) of position * frequency, angles formed in 32-bit, both times `magnitude`."""
     lib = _bind()
     _cuda(positions, "positions")
     if inv_freq.dtype != torch.float32 or not inv_freq.is_contiguous():
         raise KernelError("the rotary frequency table must be contiguous float32")
     n, half = positions.numel(), inv_freq.numel()
     table = torch.empty((n, half, 2), dtype=torch.float32, device=positions.device)
-    _check(lib, lib.gi_rope_table(table.data_ptr(), _i32(positions, "positions"), inv_freq.data_ptr(), n, 2 * half, _stream()))
+    _check(lib, lib.gi_rope_table_scaled(table.data_ptr(), _i32(positions, "positions"), inv_freq.data_ptr(), n, 2 * half,
+                                         float(magnitude), _stream()))
     return table
 
 
@@ -1450,8 +1462,12 @@ def mamba2_gate_norm(y: torch.Tensor, proj: torch.Tensor, weight: torch.Tensor, 
 
 # ------------------------------------------------------------------------------------------------
 # Routed feed-forward.
-def moe_route(h: torch.Tensor, w_router: torch.Tensor, top: int, w_shared_gate: Optional[torch.Tensor] = None):
-    """(ids int32 [tokens, top], weights float32 [tokens, top], shared gate float32 [tokens] or None)."""
+def moe_route(h: torch.Tensor, w_router: torch.Tensor, top: int, w_shared_gate: Optional[torch.Tensor] = None,
+              scores: str = "softmax"):
+    """(ids int32 [tokens, top], weights float32 [tokens, top], shared gate float32 [tokens] or None).  `scores`: "softmax"
+    (over the chosen logits) or "sigmoid" (each chosen logit's own, not renormalized)."""
+    if scores not in ("softmax", "sigmoid"):
+        raise KernelError(f"unknown kind of router weights \"{scores}\" (softmax, sigmoid)")
     lib = _bind()
     _cuda(h, "activations")
     ldh = _rows(h, "activations")
@@ -1465,10 +1481,11 @@ def moe_route(h: torch.Tensor, w_router: torch.Tensor, top: int, w_shared_gate: 
     ids = torch.empty((n, top), dtype=torch.int32, device=h.device)
     wts = torch.empty((n, top), dtype=torch.float32, device=h.device)
     sg = torch.empty((n,), dtype=torch.float32, device=h.device) if w_shared_gate is not None else None
-    _check(lib, lib.gi_moe_route(ids.data_ptr(), wts.data_ptr(), sg.data_ptr() if sg is not None else None, h.data_ptr(),
-                                 _dt(h, "activations"), ldh, w_router.data_ptr(),
-                                 w_shared_gate.data_ptr() if w_shared_gate is not None else None,
-                                 _dt(w_router, "router weights"), n, width, experts, int(top), _stream()))
+    _check(lib, lib.gi_moe_route_scored(ids.data_ptr(), wts.data_ptr(), sg.data_ptr() if sg is not None else None, h.data_ptr(),
+                                        _dt(h, "activations"), ldh, w_router.data_ptr(),
+                                        w_shared_gate.data_ptr() if w_shared_gate is not None else None,
+                                        _dt(w_router, "router weights"), n, width, experts, int(top),
+                                        1 if scores == "sigmoid" else 0, _stream()))
     return ids, wts, sg
 
 
@@ -1486,13 +1503,35 @@ def moe_plan(ids: torch.Tensor, experts: int):
     return offsets, perm, inv
 
 
-def moe_gather_rows(h: torch.Tensor, perm: torch.Tensor, top: int) -> torch.Tensor:
-    """The step's rows in the order of the sort by expert: out[r] = h[perm[r] // top]."""
+def moe_gather_rows(h: torch.Tensor, perm: torch.Tensor, top: int, scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The step's rows in the order of the sort by expert: out[r] = h[perm[r] // top], times scale[perm[r]] where `scale`
+    (float32, one number per entry: the router's weights) is given."""
     lib = _bind()
     _cuda(h, "activations")
+    if scale is not None and (scale.dtype != torch.float32 or scale.numel() != perm.numel() or not scale.is_contiguous()):
+        raise KernelError("the rows' scales must be contiguous float32, one per entry")
     out = torch.empty((perm.numel(), h.shape[1]), dtype=h.dtype, device=h.device)
-    _check(lib, lib.gi_moe_gather_rows(out.data_ptr(), h.data_ptr(), _dt(h, "activations"), _rows(h, "activations"),
-                                       _i32(perm, "permutation"), perm.numel(), int(top), h.shape[1], _stream()))
+    _check(lib, lib.gi_moe_gather_rows_scaled(out.data_ptr(), h.data_ptr(), _dt(h, "activations"), _rows(h, "activations"),
+                                              _i32(perm, "permutation"), scale.data_ptr() if scale is not None else None,
+                                              perm.numel(), int(top), h.shape[1], _stream()))
+    return out
+
+
+def moe_rows_product(rows: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, act: Optional[str] = None) -> torch.Tensor:
+    """out[r] = W_e rows[r] for rows already sorted by expert (`offsets` on the device), `w` [experts, n, k].  `act` None:
+    the sums as float32; "relu2": relu(sum)^2 in the rows' type (an ungated expert's hidden layer)."""
+    lib = _bind()
+    _cuda(rows, "sorted rows")
+    experts, n, k = w.shape
+    if act not in (None, "relu2"):
+        raise KernelError(f"unknown activation \"{act}\" (relu2)")
+    if rows.shape[1] != k or not w.is_contiguous():
+        raise KernelError(f"expert weights {tuple(w.shape)} do not fit rows of {rows.shape[1]}")
+    entries = rows.shape[0]
+    out = torch.empty((entries, n), dtype=torch.float32 if act is None else rows.dtype, device=rows.device)
+    _check(lib, lib.gi_moe_gemm_rows(out.data_ptr(), rows.data_ptr(), _dt(rows, "sorted rows"), _rows(rows, "sorted rows"),
+                                     w.data_ptr(), _dt(w, "expert weights"), w.stride(0), _i32(offsets, "offsets"), entries,
+                                     experts, n, k, 0 if act is None else 1, _stream()))
     return out
 
 
@@ -1550,18 +1589,171 @@ def moe_experts_by_expert(rows: torch.Tensor, w_gate_up: torch.Tensor, w_down: t
     return out
 
 
-def moe_combine(residual: torch.Tensor, down: torch.Tensor, inv: torch.Tensor, wts: torch.Tensor,
+def moe_combine(residual: torch.Tensor, down: torch.Tensor, inv: torch.Tensor, wts: Optional[torch.Tensor],
                 shared: Optional[torch.Tensor] = None, shared_gate: Optional[torch.Tensor] = None) -> None:
-    """residual[t] += sum_k wts[t, k] * down[inv[t, k]] (+ shared_gate[t] * shared[t])."""
+    """residual[t] += sum_k wts[t, k] * down[inv[t, k]] (+ shared_gate[t] * shared[t]); `wts` None: every weight 1."""
     lib = _bind()
     _cuda(residual, "residual stream")
     n, width = residual.shape
-    top = wts.shape[1]
+    top = inv.numel() // max(n, 1)
     if residual.dtype != torch.float32 or not residual.is_contiguous() or down.dtype != torch.float32 or down.shape[1] != width:
         raise KernelError("expert combine: float32 rows of the stream's width are wanted")
     if shared is not None and (shared.dtype != torch.float32 or tuple(shared.shape) != (n, width) or not shared.is_contiguous()
                                or shared_gate is None):
         raise KernelError("expert combine: the shared expert's output must be float32 [tokens, width] with its gate")
-    _check(lib, lib.gi_moe_combine(residual.data_ptr(), down.data_ptr(), _i32(inv, "inverse permutation"), wts.data_ptr(),
+    _check(lib, lib.gi_moe_combine(residual.data_ptr(), down.data_ptr(), _i32(inv, "inverse permutation"),
+                                   wts.data_ptr() if wts is not None else None,
                                    shared.data_ptr() if shared is not None else None,
                                    shared_gate.data_ptr() if shared is not None else None, n, width, top, _stream()))
+
+
+# ---- layers with a latent in place of keys and values per head --------------------------------------------------------
+def layernorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
+              rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """(x - mean) / sqrt(var + eps) * weight per row of the float32 matrix `x` (statistics in 32-bit)."""
+    lib = _bind()
+    _cuda(x, "layernorm input")
+    if x.dtype != torch.float32 or x.dim() != 2 or not x.is_contiguous():
+        raise KernelError("layernorm input must be a contiguous float32 [rows, width] matrix")
+    d = x.shape[1]
+    if weight.numel() != d or not weight.is_contiguous():
+        raise KernelError(f"layernorm weight has {weight.numel()} values, the rows are {d} wide")
+    n = x.shape[0] if rows is None else rows.numel()
+    out = torch.empty((n, d), dtype=out_dtype, device=x.device)
+    _check(lib, lib.gi_layernorm(out.data_ptr(), _dt(out, "layernorm output"), x.data_ptr(), weight.data_ptr(),
+                                 _dt(weight, "layernorm weight"), _i32(rows, "rows"), n, d, float(eps), _stream()))
+    return out
+
+
+def bias_act(rows: torch.Tensor, bias: Optional[torch.Tensor], act: Optional[str] = None,
+             residual: Optional[torch.Tensor] = None, residual_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """act(rows + bias) in the rows' type (`act` None or "relu2": relu squared); with `residual` (float32 rows of the
+    stream) its rows also get `residual_bias` added, in the same launch."""
+    lib = _bind()
+    _cuda(rows, "rows")
+    ld = _rows(rows, "rows")
+    n, f = rows.shape
+    if act not in (None, "relu2"):
+        raise KernelError(f"unknown activation \"{act}\" (relu2)")
+    wd = bias if bias is not None else residual_bias
+    if bias is not None and (bias.numel() != f or not bias.is_contiguous()):
+        raise KernelError(f"the bias has {bias.numel()} values, the rows are {f} wide")
+    d = 0
+    if residual is not None:
+        _cuda(residual, "residual stream")
+        d = residual.shape[1]
+        if (residual.dtype != torch.float32 or not residual.is_contiguous() or residual.shape[0] != n or residual_bias is None
+                or residual_bias.numel() != d or not residual_bias.is_contiguous() or (bias is not None and residual_bias.dtype != bias.dtype)):
+            raise KernelError("the stream's rows must be contiguous float32, one per row, with a bias of their width and the other bias's type")
+    out = torch.empty((n, f), dtype=rows.dtype, device=rows.device)
+    _check(lib, lib.gi_bias_act(out.data_ptr(), rows.data_ptr(), _dt(rows, "rows"), ld, bias.data_ptr() if bias is not None else None,
+                                _dt(wd, "bias") if wd is not None else F32, n, f, 0 if act is None else 1,
+                                residual.data_ptr() if residual is not None else None,
+                                residual_bias.data_ptr() if residual is not None else None, d, _stream()))
+    return out
+
+
+def latent_prepare(rows: torch.Tensor, w_query_norm: Optional[torch.Tensor], w_latent_norm: torch.Tensor, eps: float,
+                   table: Optional[torch.Tensor], rot: int, positions: torch.Tensor, slots: torch.Tensor, memory,
+                   q_rank: int, rank: int, rot_dim: int) -> Optional[torch.Tensor]:
+    """From rows [query latent (q_rank) | latent (rank) | rotary key part (rot_dim)]: the RMS-normed query latent (returned,
+    in the rows' type; None when q_rank is 0), and the token's cache row [RMS-normed latent | key part, its first `rot`
+    numbers turned in neighbouring pairs by `table`] written into `memory`'s pages."""
+    lib = _bind()
+    _cuda(rows, "latent rows")
+    ld = _rows(rows, "latent rows")
+    n = rows.shape[0]
+    if rows.shape[1] != q_rank + rank + rot_dim:
+        raise KernelError(f"latent rows are {rows.shape[1]} wide, wanted {q_rank + rank + rot_dim}")
+    write = bool(memory.writes and memory.k is not None)
+    if write and (memory.k.dtype != rows.dtype or tuple(memory.k.shape[1:]) != (1, 64, rank + rot_dim) or not memory.k.is_contiguous()):
+        raise KernelError(f"the latent cache must be contiguous {rows.dtype} [pages, 1, 64, {rank + rot_dim}], got {memory.k.dtype} {tuple(memory.k.shape)}")
+    if w_latent_norm.numel() != rank or (q_rank and (w_query_norm is None or w_query_norm.numel() != q_rank or w_query_norm.dtype != w_latent_norm.dtype)):
+        raise KernelError("the latents' norm weights do not fit their sizes")
+    cq = torch.empty((n, q_rank), dtype=rows.dtype, device=rows.device) if q_rank else None
+    bt = memory.block_table
+    _check(lib, lib.gi_latent_prepare(
+        cq.data_ptr() if cq is not None else None, rows.data_ptr(), _dt(rows, "latent rows"), ld,
+        w_query_norm.data_ptr() if q_rank else None, w_latent_norm.data_ptr(), _dt(w_latent_norm, "norm weights"), float(eps),
+        table.data_ptr() if table is not None else None, int(rot), _i32(positions, "positions"), _i32(slots, "slots"),
+        _i32(bt, "block table"), bt.shape[1] if bt is not None else 0, memory.k.data_ptr() if write else None, n, q_rank, rank,
+        rot_dim, int(write), _stream()))
+    return cq
+
+
+def latent_query_rot(qa: torch.Tensor, q: torch.Tensor, table: Optional[torch.Tensor], rot: int, n_heads: int, dim: int,
+                     rot_dim: int, rank: int) -> None:
+    """qa[t, h, rank:] = q[t, h, dim:] with its first `rot` numbers turned; q rows [heads][dim + rot_dim], qa rows
+    [heads][rank + rot_dim]."""
+    lib = _bind()
+    _cuda(q, "queries")
+    if q.dtype != qa.dtype or q.shape[1] != n_heads * (dim + rot_dim) or qa.shape[1] != n_heads * (rank + rot_dim) or q.shape[0] != qa.shape[0]:
+        raise KernelError("latent queries: rows of the wrong sizes")
+    _check(lib, lib.gi_latent_query_rot(qa.data_ptr(), _rows(qa, "latent queries"), q.data_ptr(), _rows(q, "queries"),
+                                        _dt(q, "queries"), table.data_ptr() if table is not None else None, int(rot), q.shape[0],
+                                        n_heads, dim, rot_dim, rank, _stream()))
+
+
+def bmm_heads(out: torch.Tensor, out_head_stride: int, a: torch.Tensor, a_head_stride: int, w: torch.Tensor, n: int, k: int,
+              k_stride: int = 1, row_stride: Optional[int] = None) -> None:
+    """out[t, h * out_head_stride + j] = sum_i a[t, h * a_head_stride + i] * w[h][j, i] for j < n, i < k and every head h of
+    `w` [heads, ...]: element (j, i) of a head's matrix sits at j * row_stride + i * k_stride (default: [n, k] row-major)."""
+    lib = _bind()
+    _cuda(a, "rows")
+    if a.dtype != out.dtype or a.shape[0] != out.shape[0]:
+        raise KernelError("per-head product: rows and outputs must share type and count")
+    heads = w.shape[0]
+    if not w.is_contiguous():
+        raise KernelError("per-head product: the matrices must be contiguous")
+    ldw = int(row_stride if row_stride is not None else k)
+    _check(lib, lib.gi_bmm_heads(out.data_ptr(), _rows(out, "outputs"), int(out_head_stride), a.data_ptr(), _rows(a, "rows"),
+                                 int(a_head_stride), _dt(a, "rows"), w.data_ptr(), _dt(w, "matrices"), w.stride(0), ldw,
+                                 int(k_stride), a.shape[0], int(n), int(k), heads, int(TUNE["bmm_heads_tc"]), _stream()))
+
+
+def attn_latent_decode_plan(n_seqs: int, max_kv_len: int, sm_count: int, n_heads: int, rank: int, rot_dim: int, dtype: torch.dtype):
+    """(kernel, slices in the launch, tiles per slice) for one-token steps over a latent cache: slices of eight 32-key
+    tiles of each sequence's own span, so that a sequence's sums are formed in the same order whatever the step holds."""
+    tiles = (max_kv_len + 31) // 32
+    return "plain", max(1, (tiles + OWN_LENGTH_TILES - 1) // OWN_LENGTH_TILES), OWN_LENGTH_TILES
+
+
+def attention_latent(qa: torch.Tensor, memory, step, n_heads: int, rank: int, rot_dim: int, scale: float, out: torch.Tensor,
+                     plan=None) -> torch.Tensor:
+    """Causal attention of all heads over one shared row per position: `memory.k` holds [latent (rank) | rotary key part
+    (rot_dim)] per position, a head's query row in `qa` has the same layout (its unrotated part already carried onto the
+    latent), the score is their product times `scale`, and the value is the row's latent: out [tokens, heads * rank]."""
+    if memory.k is None:
+        raise KernelError("attention needs a cache to read from")
+    hd = rank + rot_dim
+    if qa.shape[1] != n_heads * hd or out.shape[1] != n_heads * rank:
+        raise KernelError("latent attention: rows of the wrong sizes")
+    if step.is_decode:
+        if plan is None:
+            plan = attn_latent_decode_plan(step.n_seqs, step.max_kv_len, step.sm_count, n_heads, rank, rot_dim, qa.dtype)
+        _, n_splits, own_tiles = plan
+        part_o = part_ml = None
+        if n_splits > 1:
+            part_o = torch.empty((step.n_seqs * n_heads * n_splits * rank,), dtype=torch.float32, device=qa.device)
+            part_ml = torch.empty((step.n_seqs * n_heads * n_splits * 2,), dtype=torch.float32, device=qa.device)
+        lib = _bind()
+        _cuda(qa, "queries")
+        if memory.k.dtype != qa.dtype or out.dtype != qa.dtype:
+            raise KernelError("queries, cache and attention output must share a dtype")
+        _check(lib, lib.gi_attn_decode_generic_ex2(
+            out.data_ptr(), _rows(out, "attention output"), part_o.data_ptr() if part_o is not None else None,
+            part_ml.data_ptr() if part_ml is not None else None, qa.data_ptr(), _rows(qa, "queries"), _dt(qa, "queries"),
+            memory.k.data_ptr(), memory.k.data_ptr(), _i32(memory.block_table, "block table"), memory.block_table.shape[1],
+            _i32(step.seq_slots, "slots"), _i32(step.seq_lens, "lengths"), step.n_seqs, n_heads, 1, hd, float(scale), 0,
+            int(n_splits), int(own_tiles), rank, 0.0, None, 0, hd, _stream()), 2 if n_splits > 1 else 1)
+        return out
+    lib = _bind()
+    _cuda(qa, "queries")
+    if memory.k.dtype != qa.dtype or out.dtype != qa.dtype:
+        raise KernelError("queries, cache and attention output must share a dtype")
+    _check(lib, lib.gi_attn_prefill_generic_ex2(
+        out.data_ptr(), _rows(out, "attention output"), qa.data_ptr(), _rows(qa, "queries"), _dt(qa, "queries"),
+        memory.k.data_ptr(), memory.k.data_ptr(), _i32(memory.block_table, "block table"), memory.block_table.shape[1],
+        _i32(step.cu_seqlens, "cu_seqlens"), _i32(step.seq_slots, "slots"), _i32(step.seq_pos0, "start positions"), step.n_seqs,
+        step.max_q_len, n_heads, 1, hd, float(scale), 0, rank, 0.0, None, 0, hd, _stream()))
+    return out

@@ -8,6 +8,10 @@ keys "gate", "up", "down".
 
 The same layer with another activation in place of silu (`params["activation"]`: "silu", the default, or
 "gelu_tanh", 0.5 g (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3)))) is registered as "gated_mlp".
+
+"mlp": the ungated layer residual += Wdown act(Wup h + b_up) + b_down, with `activation` "relu2" (relu(z)^2) and, with
+`bias` (the default), a bias on both products.  Tensor names: prefix + "mlp.{up,down}" and the same + ".b" for the biases,
+unless `params["tensor_names"]` gives others for the keys "up", "up_bias", "down", "down_bias".
 """
 from __future__ import annotations
 
@@ -63,4 +67,43 @@ class SwiGlu(FeedForward):
             else:
                 gu = linear(h, self.w_gate_up, out_dtype=self.rt.dtype)
                 act = ops.silu_mul(gu) if self.activation == "silu" else ops.act_mul(gu, self.activation)
+            linear(act, self.w_down, out=residual, accumulate=True)
+
+
+@register("feed_forward", "mlp")
+class Mlp(FeedForward):
+    def __init__(self, params, prefix=""):
+        super().__init__(params, prefix)
+        self.hidden = int(params["hidden_size"])
+        self.inter = int(params["intermediate_size"])
+        self.activation = str(params.get("activation", "relu2"))
+        self.bias = bool(params.get("bias", True))
+        if self.activation != "relu2":
+            raise ValueError(f"unknown activation \"{self.activation}\" (relu2)")
+        d = {"up": "mlp.up", "up_bias": "mlp.up.b", "down": "mlp.down", "down_bias": "mlp.down.b"}
+        self.names = {k: self.tensor_name(k, v) for k, v in d.items()}
+
+    def weights(self) -> List[WeightSpec]:
+        n = self.names
+        out = [WeightSpec(n["up"], (self.inter, self.hidden)), WeightSpec(n["down"], (self.hidden, self.inter))]
+        if self.bias:
+            out += [WeightSpec(n["up_bias"], (self.inter,)), WeightSpec(n["down_bias"], (self.hidden,))]
+        return out
+
+    def bind(self, tensors, rt) -> None:
+        super().bind(tensors, rt)
+        self.w_up, self.w_down = rt.place(tensors[self.names["up"]]), rt.place(tensors[self.names["down"]])
+        self.b_up = self.b_down = None
+        if self.bias:
+            bu, bd = rt.place(tensors[self.names["up_bias"]]), rt.place(tensors[self.names["down_bias"]])
+            if bu.dtype != bd.dtype:
+                bu, bd = bu.to(torch.float32), bd.to(torch.float32)
+            self.b_up, self.b_down = bu, bd
+
+    def forward(self, h, residual, step) -> None:
+        with ops.bucket("ffn matmul"):
+            up = linear(h, self.w_up, out_dtype=self.rt.dtype)
+            if self.bias:
+                ops.settle(residual)         # the rows get the output's bias from a plain kernel, which adds no partial sums
+            act = ops.bias_act(up, self.b_up, self.activation, residual if self.bias else None, self.b_down)
             linear(act, self.w_down, out=residual, accumulate=True)

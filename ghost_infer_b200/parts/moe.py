@@ -12,6 +12,11 @@ the tensor-core products the dense feed-forward uses, its gate and up rows inter
 
 Tensor names: prefix + "mlp.router", "mlp.e<i>.{gate,up,down}", "mlp.shared.{gate,up,down,sg}" unless
 `params["tensor_names"]` replaces the stems "router", "expert" (a format with `{i}`) or "shared".
+
+"scored_experts" is the routed layer in another form: the experts are ungated, W_down,e relu(W_up,e x)^2 (`activation`
+"relu2"); a chosen expert's weight is `scores` "sigmoid": the sigmoid of its own logit, not renormalized (or "softmax":
+as above); and with `weight_on` "input" the weight multiplies what the expert reads, out = sum_e expert_e(w_e h), instead
+of what it returns ("output").  It has no shared expert.  Tensors: "mlp.router", "mlp.e<i>.{up,down}".
 """
 from __future__ import annotations
 
@@ -122,3 +127,71 @@ class RoutedExperts(FeedForward):
                 shared = linear(act, self.w_shared_down, out_dtype=torch.float32)
             ops.settle(residual)
             ops.moe_combine(residual, down, inv, wts, shared, sgate)
+
+
+@register("feed_forward", "scored_experts")
+class ScoredExperts(FeedForward):
+    def __init__(self, params, prefix=""):
+        super().__init__(params, prefix)
+        self.hidden = int(params["hidden_size"])
+        self.experts = int(params["experts"])
+        self.top = int(params["top"])
+        self.ff = int(params["expert_ff"])
+        self.activation = str(params.get("activation", "relu2"))
+        self.scores = str(params.get("scores", "sigmoid"))
+        self.weight_on = str(params.get("weight_on", "input"))
+        if not (1 <= self.top <= self.experts):
+            raise ValueError(f"a token cannot use {self.top} of {self.experts} experts")
+        if self.activation != "relu2" or self.scores not in ("sigmoid", "softmax") or self.weight_on not in ("input", "output"):
+            raise ValueError("scored experts: activation relu2; scores sigmoid or softmax; weight_on input or output")
+        self.router_name = self.tensor_name("router", "mlp.router")
+        self.expert_stem = self.tensor_name("expert", "mlp.e{i}.")
+
+    def _expert(self, i: int, what: str) -> str:
+        return self.expert_stem.format(i=i) + what
+
+    def weights(self) -> List[WeightSpec]:
+        out = [WeightSpec(self.router_name, (self.experts, self.hidden))]
+        for i in range(self.experts):
+            out += [WeightSpec(self._expert(i, "up"), (self.ff, self.hidden)), WeightSpec(self._expert(i, "down"), (self.hidden, self.ff))]
+        return out
+
+    def bind(self, tensors, rt) -> None:
+        super().bind(tensors, rt)
+        self.w_router = rt.place(tensors[self.router_name])
+        self.w_up = rt.place(torch.stack([tensors[self._expert(i, "up")] for i in range(self.experts)]))       # [E, f, d]
+        self.w_down = rt.place(torch.stack([tensors[self._expert(i, "down")] for i in range(self.experts)]))   # [E, d, f]
+        if self.w_up.dtype != self.w_down.dtype:
+            self.w_up, self.w_down = self.w_up.float(), self.w_down.float()
+
+    # rows per expert, on average, from which a prompt step takes the tensor-core products expert by expert
+    ROWS_FOR_TENSOR_CORES = 96
+
+    def _by_expert(self, h, step) -> bool:
+        return (not step.is_decode and h.dtype == torch.bfloat16 and self.w_up.dtype == torch.bfloat16 and self.hidden % 8 == 0
+                and self.ff % 8 == 0 and h.shape[0] * self.top >= self.ROWS_FOR_TENSOR_CORES * self.experts
+                and not torch.cuda.is_current_stream_capturing())
+
+    def forward(self, h, residual, step) -> None:
+        with ops.bucket("router"):
+            ids, wts, _ = ops.moe_route(h, self.w_router, self.top, None, scores=self.scores)
+            offsets, perm, inv = ops.moe_plan(ids, self.experts)
+        with ops.bucket("experts"):
+            # the rows in the order of the sort, each times its entry's weight where the weight goes onto the input
+            rows = ops.moe_gather_rows(h, perm, self.top, wts.view(-1) if self.weight_on == "input" else None)
+            if self._by_expert(h, step):
+                # enough rows per expert: the host reads the experts' offsets back (one wait) and every expert's stretch
+                # goes through the products the dense layers use
+                offs = offsets.cpu().tolist()
+                down = torch.empty((rows.shape[0], self.hidden), dtype=torch.float32, device=h.device)
+                for e in range(self.experts):
+                    lo, hi = offs[e], offs[e + 1]
+                    if hi > lo:
+                        up = linear(rows[lo:hi], self.w_up[e], out_dtype=h.dtype)
+                        linear(ops.bias_act(up, None, self.activation), self.w_down[e], out=down[lo:hi])
+            else:
+                hidden = ops.moe_rows_product(rows, self.w_up, offsets, act=self.activation)
+                down = ops.moe_rows_product(hidden, self.w_down, offsets)
+        with ops.bucket("ffn matmul"):
+            ops.settle(residual)
+            ops.moe_combine(residual, down, inv, wts if self.weight_on == "output" else None)

@@ -2,6 +2,11 @@
 
 eps sits inside the square root and the weight multiplies last, with no bias and no "+1"
 (src/model.rs:919-928, src/cuda.rs:505-515).
+
+"layernorm": y = (x - mean(x)) / sqrt(mean((x - mean(x))^2) + eps) * w, with a weight and no bias, also 32-bit.
+
+`forward(x, rows=None, out_dtype=None)`: `out_dtype` None is the step's activation type; a model that norms its
+embeddings asks for float32, the stream's own type.
 """
 from __future__ import annotations
 
@@ -30,6 +35,27 @@ class RmsNorm(Norm):
         super().bind(tensors, rt)
         self.weight = rt.place(tensors[self.tensor_name("weight", "weight")])
 
-    def forward(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         with ops.bucket("norm"):
-            return ops.rmsnorm(x, self.weight, self.eps, self.rt.dtype, rows=rows)
+            return ops.rmsnorm(x, self.weight, self.eps, out_dtype or self.rt.dtype, rows=rows)
+
+
+@register("norm", "layernorm")
+class LayerNorm(Norm):
+    settles_pending = False     # whoever calls it settles a deferred product's partial sums first
+
+    def __init__(self, params, prefix=""):
+        super().__init__(params, prefix)
+        self.size = int(params["size"])
+        self.eps = float(params["eps"])
+
+    def weights(self) -> List[WeightSpec]:
+        return [WeightSpec(self.tensor_name("weight", "weight"), (self.size,), "ones")]
+
+    def bind(self, tensors, rt) -> None:
+        super().bind(tensors, rt)
+        self.weight = rt.place(tensors[self.tensor_name("weight", "weight")])
+
+    def forward(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        with ops.bucket("norm"):
+            return ops.layernorm(x, self.weight, self.eps, out_dtype or self.rt.dtype, rows=rows)

@@ -8,6 +8,12 @@ here that table comes from config.json's rope_scaling with the llama3 rule: a pa
 2 pi / inv_freq is shorter than original_max / high_freq_factor keeps its frequency, one longer than
 original_max / low_freq_factor has it divided by `factor`, and those between are blended linearly
 in original_max / wavelength.  The table is computed once in 64-bit and rounded to 32-bit.
+
+The YaRN rule (`scaling["rope_type"] == "yarn"`, with `factor`, `original`, `fast`, `slow`): pair i of a rotation over
+n numbers makes original * f_i / (2 pi) turns over the original length; idx(t) = n ln(original / (2 pi t)) / (2 ln base)
+is the (fractional) pair index that makes t turns.  With lo = max(floor(idx(fast)), 0), hi = min(ceil(idx(slow)), n - 1)
+and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1) the frequency becomes (f_i / factor) ramp_i + f_i (1 - ramp_i),
+and cosine and sine are both multiplied by 0.1 ln(factor) + 1 (`Rotary.magnitude`; `scaling["magnitude"]` overrides it).
 """
 from __future__ import annotations
 
@@ -25,9 +31,18 @@ def rotary_inv_freq(rotary_dim: int, theta: float, scaling: Optional[Mapping]) -
     """float32 [rotary_dim / 2]."""
     half = rotary_dim // 2
     out = []
+    yarn = scaling is not None and scaling.get("rope_type", "llama3") == "yarn"
+    if yarn:
+        factor, orig = float(scaling["factor"]), float(scaling["original"])
+        idx = lambda turns: rotary_dim * math.log(orig / (2.0 * math.pi * turns)) / (2.0 * math.log(theta))
+        lo = max(math.floor(idx(float(scaling["fast"]))), 0)
+        hi = min(math.ceil(idx(float(scaling["slow"]))), rotary_dim - 1)
     for i in range(half):
         f = theta ** (-(2.0 * i) / rotary_dim)
-        if scaling is not None:
+        if yarn:
+            ramp = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+            f = f / factor * ramp + f * (1.0 - ramp)
+        elif scaling is not None:
             factor = float(scaling["factor"])
             low = float(scaling["low_freq_factor"])
             high = float(scaling["high_freq_factor"])
@@ -57,10 +72,14 @@ class Rotary(PositionEncoding):
         if self.rotary_dim % 2 or self.rotary_dim > self.head_dim:
             raise ValueError(f"rotary_dim {self.rotary_dim} must be even and at most head_dim {self.head_dim}")
         scaling = params.get("scaling")
-        if scaling is not None and scaling.get("rope_type", "llama3") != "llama3":
+        if scaling is not None and scaling.get("rope_type", "llama3") not in ("llama3", "yarn"):
             raise ValueError(f"rotary scaling of type {scaling.get('rope_type')!r} is not supported")
         self.scaling = scaling
         self.inv_freq_host = rotary_inv_freq(self.rotary_dim, self.theta, scaling)
+        # what multiplies cosine and sine alike (1 unless the scaling rule stretches the rotated vectors)
+        self.magnitude = 1.0
+        if scaling is not None and scaling.get("rope_type") == "yarn":
+            self.magnitude = float(scaling.get("magnitude", 0.1 * math.log(float(scaling["factor"])) + 1.0))
 
     def bind(self, tensors, rt) -> None:
         super().bind(tensors, rt)
@@ -73,9 +92,13 @@ class Rotary(PositionEncoding):
         # serves every layer that rotates the same way
         table = step.shared.get(self.table_key)
         if table is None:
-            table = ops.rope_table(step.positions, self.inv_freq)
+            table = ops.rope_table(step.positions, self.inv_freq, self.magnitude)
             step.shared[self.table_key] = table
         return table
+
+    def table(self, step):
+        """float32 [tokens, pairs, 2]: magnitude * (cos, sin) of every token's angles, made once per step."""
+        return self._table(step)
 
     def project_and_store(self, h, w_qkv, step, memory, n_heads, n_kv_heads, head_dim):
         # a prompt step's product on the tensor cores rotates its own rows: every thread of its epilogue holds one token's row

@@ -82,6 +82,8 @@ class ModelSpec:
     final_norm_prefix: str = "model.norm."
     head_prefix: str = "lm_head."
     ignorable_tensors: Tuple[str, ...] = ()     # names a weights file may carry although no part uses them
+    embedding_norm: Optional[PartSpec] = None   # a norm on the embedded tokens, before the first layer (32-bit result)
+    embedding_norm_prefix: str = "model.embed_norm."
 
     def validate(self) -> None:
         for i, e in enumerate(self.schedule):
