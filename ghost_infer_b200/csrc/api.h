@@ -238,6 +238,16 @@ int gi_latent_query_rot(void* qa, long ldqa, const void* q, long ldq, int dtype,
 // a's type.  tensor_cores: bfloat16 operands with kstride 1 take `mma.sync`.
 int gi_bmm_heads(void* out, long ldo, long ohs, const void* a, long lda, long ahs, int dtype, const void* w, int w_dtype,
                  long whs, long ldw, long kstride, int M, int N, int K, int heads, int tensor_cores, void* stream);
+// Causal attention of n_heads heads over one shared row per position, on tensor cores (bfloat16): the cache holds rows of dk
+// numbers in pages [page][64][dk]; q rows are [heads][dk]; score = q . row * scale; the value is the row's first dv numbers;
+// out rows [heads][dv].  cu_seqlens given: a prompt step (seq_pos0: cached lengths before it).  cu_seqlens null: a one-token
+// step (seq_lens: lengths including the token) cut into n_splits slices of the context (own_tiles > 0: that many 64-key
+// tiles of each sequence's own span per slice), merged inside; part_o holds dv floats and part_ml 2 per (sequence, head,
+// slice).  dk and dv multiples of 8, dk <= 576, dv <= 512.
+int gi_attn_latent_tc(void* out, long ldo, float* part_o, float* part_ml, const void* q, long ldq, const void* kcache,
+                      const int* block_table, int max_pages, const int* cu_seqlens, const int* seq_slots, const int* seq_pos0,
+                      const int* seq_lens, int n_seqs, int max_q_len, int n_heads, int dk, int dv, float scale, int n_splits,
+                      int own_tiles, void* stream);
 // table[t, i] = magnitude * (cos, sin)(positions[t] * inv_freq[i])
 int gi_rope_table_scaled(float* table, const int* positions, const float* inv_freq, int n_tokens, int rot, float magnitude,
                          void* stream);

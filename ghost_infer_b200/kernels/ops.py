@@ -98,6 +98,7 @@ def _bind():
         "gi_latent_query_rot": [P, L, P, L, I, P, I, I, I, I, I, I, P],
         "gi_bmm_heads": [P, L, L, P, L, L, I, P, I, L, L, L, I, I, I, I, I, P],
         "gi_rope_table_scaled": [P, P, P, I, I, F, P],
+        "gi_attn_latent_tc": [P, L, P, P, P, L, P, P, I, P, P, P, P, I, I, I, I, I, F, I, I, P],
     }
     for name, argtypes in sigs.items():
         fn = getattr(lib, name)
@@ -1711,9 +1712,22 @@ def bmm_heads(out: torch.Tensor, out_head_stride: int, a: torch.Tensor, a_head_s
                                  int(k_stride), a.shape[0], int(n), int(k), heads, int(TUNE["bmm_heads_tc"]), _stream()))
 
 
+def attn_latent_tc_ok(dtype: torch.dtype, rank: int, rot_dim: int) -> bool:
+    """Whether the tensor-core kernel takes a latent cache of these sizes: bfloat16, rows and values multiples of 8,
+    rows up to 576 and values up to 512 numbers."""
+    return bool(TUNE["attn_latent_tc"] and dtype == torch.bfloat16 and rank % 8 == 0 and rot_dim % 8 == 0
+                and rank + rot_dim <= 576 and rank <= 512)
+
+
 def attn_latent_decode_plan(n_seqs: int, max_kv_len: int, sm_count: int, n_heads: int, rank: int, rot_dim: int, dtype: torch.dtype):
-    """(kernel, slices in the launch, tiles per slice) for one-token steps over a latent cache: slices of eight 32-key
-    tiles of each sequence's own span, so that a sequence's sums are formed in the same order whatever the step holds."""
+    """(kernel, slices in the launch, tiles per slice) for one-token steps over a latent cache.
+    "tensor cores" (bfloat16, sizes the kernel takes): every context cut into equal slices of 64-key tiles, as many as
+    fill the GPU once.  "plain": slices of eight 32-key tiles of each sequence's own span, so that a sequence's sums are
+    formed in the same order whatever the step holds."""
+    if attn_latent_tc_ok(dtype, rank, rot_dim):
+        tiles = (max_kv_len + 63) // 64
+        blocks = n_seqs * ((n_heads + 63) // 64)
+        return "tensor cores", max(1, min(tiles, (sm_count + blocks - 1) // blocks)), 0
     tiles = (max_kv_len + 31) // 32
     return "plain", max(1, (tiles + OWN_LENGTH_TILES - 1) // OWN_LENGTH_TILES), OWN_LENGTH_TILES
 
@@ -1728,32 +1742,48 @@ def attention_latent(qa: torch.Tensor, memory, step, n_heads: int, rank: int, ro
     hd = rank + rot_dim
     if qa.shape[1] != n_heads * hd or out.shape[1] != n_heads * rank:
         raise KernelError("latent attention: rows of the wrong sizes")
-    if step.is_decode:
-        if plan is None:
-            plan = attn_latent_decode_plan(step.n_seqs, step.max_kv_len, step.sm_count, n_heads, rank, rot_dim, qa.dtype)
-        _, n_splits, own_tiles = plan
-        part_o = part_ml = None
-        if n_splits > 1:
-            part_o = torch.empty((step.n_seqs * n_heads * n_splits * rank,), dtype=torch.float32, device=qa.device)
-            part_ml = torch.empty((step.n_seqs * n_heads * n_splits * 2,), dtype=torch.float32, device=qa.device)
-        lib = _bind()
-        _cuda(qa, "queries")
-        if memory.k.dtype != qa.dtype or out.dtype != qa.dtype:
-            raise KernelError("queries, cache and attention output must share a dtype")
-        _check(lib, lib.gi_attn_decode_generic_ex2(
-            out.data_ptr(), _rows(out, "attention output"), part_o.data_ptr() if part_o is not None else None,
-            part_ml.data_ptr() if part_ml is not None else None, qa.data_ptr(), _rows(qa, "queries"), _dt(qa, "queries"),
-            memory.k.data_ptr(), memory.k.data_ptr(), _i32(memory.block_table, "block table"), memory.block_table.shape[1],
-            _i32(step.seq_slots, "slots"), _i32(step.seq_lens, "lengths"), step.n_seqs, n_heads, 1, hd, float(scale), 0,
-            int(n_splits), int(own_tiles), rank, 0.0, None, 0, hd, _stream()), 2 if n_splits > 1 else 1)
-        return out
     lib = _bind()
     _cuda(qa, "queries")
     if memory.k.dtype != qa.dtype or out.dtype != qa.dtype:
         raise KernelError("queries, cache and attention output must share a dtype")
+    if tuple(memory.k.shape[1:]) != (1, 64, hd) or not memory.k.is_contiguous():
+        raise KernelError(f"the latent cache must be contiguous [pages, 1, 64, {hd}], got {tuple(memory.k.shape)}")
+    bt = memory.block_table
+    tc = (attn_latent_tc_ok(qa.dtype, rank, rot_dim) and qa.stride(0) % 8 == 0 and qa.data_ptr() % 16 == 0
+          and out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0)
+    if step.is_decode:
+        if plan is None:
+            plan = attn_latent_decode_plan(step.n_seqs, step.max_kv_len, step.sm_count, n_heads, rank, rot_dim, qa.dtype)
+        kind, n_splits, own_tiles = plan
+        if kind == "tensor cores" and not tc:
+            raise KernelError("latent attention: the rows do not suit the tensor-core kernel this step was planned for")
+        part_o = part_ml = None
+        if n_splits > 1:
+            part_o = torch.empty((step.n_seqs * n_heads * n_splits * rank,), dtype=torch.float32, device=qa.device)
+            part_ml = torch.empty((step.n_seqs * n_heads * n_splits * 2,), dtype=torch.float32, device=qa.device)
+        po, pml = (part_o.data_ptr(), part_ml.data_ptr()) if part_o is not None else (None, None)
+        if kind == "tensor cores":
+            _check(lib, lib.gi_attn_latent_tc(
+                out.data_ptr(), _rows(out, "attention output"), po, pml, qa.data_ptr(), _rows(qa, "queries"), memory.k.data_ptr(),
+                _i32(bt, "block table"), bt.shape[1], None, _i32(step.seq_slots, "slots"), None, _i32(step.seq_lens, "lengths"),
+                step.n_seqs, 1, n_heads, hd, rank, float(scale), int(n_splits), int(own_tiles), _stream()), 2 if n_splits > 1 else 1)
+            return out
+        _check(lib, lib.gi_attn_decode_generic_ex2(
+            out.data_ptr(), _rows(out, "attention output"), po, pml, qa.data_ptr(), _rows(qa, "queries"), _dt(qa, "queries"),
+            memory.k.data_ptr(), memory.k.data_ptr(), _i32(bt, "block table"), bt.shape[1],
+            _i32(step.seq_slots, "slots"), _i32(step.seq_lens, "lengths"), step.n_seqs, n_heads, 1, hd, float(scale), 0,
+            int(n_splits), int(own_tiles), rank, 0.0, None, 0, hd, _stream()), 2 if n_splits > 1 else 1)
+        return out
+    if tc:
+        _check(lib, lib.gi_attn_latent_tc(
+            out.data_ptr(), _rows(out, "attention output"), None, None, qa.data_ptr(), _rows(qa, "queries"), memory.k.data_ptr(),
+            _i32(bt, "block table"), bt.shape[1], _i32(step.cu_seqlens, "cu_seqlens"), _i32(step.seq_slots, "slots"),
+            _i32(step.seq_pos0, "start positions"), None, step.n_seqs, step.max_q_len, n_heads, hd, rank, float(scale), 1, 0,
+            _stream()))
+        return out
     _check(lib, lib.gi_attn_prefill_generic_ex2(
         out.data_ptr(), _rows(out, "attention output"), qa.data_ptr(), _rows(qa, "queries"), _dt(qa, "queries"),
-        memory.k.data_ptr(), memory.k.data_ptr(), _i32(memory.block_table, "block table"), memory.block_table.shape[1],
+        memory.k.data_ptr(), memory.k.data_ptr(), _i32(bt, "block table"), bt.shape[1],
         _i32(step.cu_seqlens, "cu_seqlens"), _i32(step.seq_slots, "slots"), _i32(step.seq_pos0, "start positions"), step.n_seqs,
         step.max_q_len, n_heads, 1, hd, float(scale), 0, rank, 0.0, None, 0, hd, _stream()))
     return out

@@ -75,13 +75,13 @@ def latent_attention(h, w, m, eps, positions=None):
     down = h @ f64("dkv").T
     c = rms_norm(down[:, :r], w["dkv.norm"], eps)
     k_rot = down[:, r:]                                                       # [T, dr], one for all heads
-    rot = m["rot"]
-    freqs, mag = rotary_frequencies(rot["dims"], rot["base"], rot.get("scaling"))
-    nrot = rot["dims"]
-    q_rot = q[:, :, dn:].copy()
-    q_rot[..., :nrot] = rotate_pairs(q_rot[..., :nrot], pos, freqs, mag)
-    k_rot = k_rot.copy()
-    k_rot[:, :nrot] = rotate_pairs(k_rot[:, :nrot], pos, freqs, mag)
+    q_rot, k_rot = q[:, :, dn:].copy(), k_rot.copy()
+    if dr:
+        rot = m["rot"]
+        freqs, mag = rotary_frequencies(rot["dims"], rot["base"], rot.get("scaling"))
+        nrot = rot["dims"]
+        q_rot[..., :nrot] = rotate_pairs(q_rot[..., :nrot], pos, freqs, mag)
+        k_rot[:, :nrot] = rotate_pairs(k_rot[:, :nrot], pos, freqs, mag)
     k = (c @ f64("uk").T).reshape(T, H, dn)
     v = (c @ f64("uv").T).reshape(T, H, dv)
     out = np.zeros((T, H, dv))
@@ -139,7 +139,9 @@ def forward(config, tensors, tokens, return_layers=False):
     x = layer_norm(emb[np.asarray(tokens)], tensors["embed.norm"], eps)
     seen = []
     for i, layer in enumerate(config["layers"]):
-        src = layer.get("weights_of", i)
+        src = i
+        while config["layers"][src].get("weights_of") is not None:       # a layer that borrows another layer's tensors
+            src = config["layers"][src]["weights_of"]
         p = f"l{src}."
         if layer["type"] != "latent_attention":
             raise ValueError(layer["type"])
@@ -156,3 +158,66 @@ def forward(config, tensors, tokens, return_layers=False):
         seen.append(x.copy())
     logits = layer_norm(x, tensors["final.norm"], eps) @ emb.T
     return (logits, np.stack(seen)) if return_layers else logits
+
+
+# ---- test models: random weights and a file of them -----------------------------------------------------------------
+def _to_bf16_values(a):
+    """Float32 values rounded to the nearest value that has 8 significant bits (ties to even), still as float32."""
+    bits = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    bits = ((bits + 0x7FFF + ((bits >> 16) & 1)) >> 16) << 16
+    return bits.astype(np.uint32).view(np.float32)
+
+
+def random_weights(config, seed=0):
+    """name -> float64 array for every tensor of `config`; all values fit bfloat16 exactly.  Layers that borrow another
+    layer's tensors get none."""
+    rng = np.random.default_rng(seed)
+    d, out = int(config["width"]), {}
+
+    def put(name, shape, std=None, mean=0.0):
+        if std is None:
+            std = 1.0 / math.sqrt(shape[-1]) if len(shape) > 1 else 0.5
+        out[name] = _to_bf16_values(rng.standard_normal(shape) * std + mean).astype(np.float64).reshape(shape)
+
+    put("embed", (int(config["vocab"]), d), 1.0)
+    put("embed.norm", (d,), 0.1, 1.0)
+    put("final.norm", (d,), 0.1, 1.0)
+    for i, layer in enumerate(config["layers"]):
+        if layer.get("weights_of") is not None:
+            continue
+        p, m = f"l{i}.", layer["mixer"]
+        H, dn, dr, dv, r, rq = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"], m["q_rank"]
+        put(p + "norm1", (d,), 0.1, 1.0)
+        put(p + "mix.dq", (rq, d)); put(p + "mix.dq.norm", (rq,), 0.1, 1.0); put(p + "mix.uq", (H * (dn + dr), rq))
+        put(p + "mix.dkv", (r + dr, d)); put(p + "mix.dkv.norm", (r,), 0.1, 1.0)
+        put(p + "mix.uk", (H * dn, r)); put(p + "mix.uv", (H * dv, r)); put(p + "mix.o", (d, H * dv))
+        mlp = layer.get("mlp")
+        if not mlp:
+            continue
+        put(p + "norm2", (d,), 0.1, 1.0)
+        if mlp["kind"] == "dense":
+            f = int(mlp["ff"])
+            put(p + "mlp.up", (f, d)); put(p + "mlp.up.b", (f,), 0.3); put(p + "mlp.down", (d, f)); put(p + "mlp.down.b", (d,), 0.3)
+        else:
+            f = int(mlp["expert"]["ff"])
+            for e in range(int(mlp["router"]["experts"])):
+                put(p + f"mlp.e{e}.up", (f, d)); put(p + f"mlp.e{e}.down", (d, f))
+            put(p + "mlp.router", (int(mlp["router"]["experts"]), d), 4.0 / math.sqrt(d))
+    return out
+
+
+def write_bf16_file(path, tensors):
+    """The tensors (bfloat16 values held in wider floats) as a safetensors file: 8 bytes of header length, the JSON header
+    (name -> dtype, shape, data_offsets), then the data."""
+    import json
+    import struct
+    header, chunks, at = {}, [], 0
+    for name, a in tensors.items():
+        raw = (np.ascontiguousarray(a, dtype=np.float32).view(np.uint32) >> 16).astype("<u2").tobytes()
+        header[name] = {"dtype": "BF16", "shape": list(np.shape(a)), "data_offsets": [at, at + len(raw)]}
+        chunks.append(raw)
+        at += len(raw)
+    head = json.dumps(header).encode()
+    head += b" " * (-len(head) % 8)
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(head)) + head + b"".join(chunks))
