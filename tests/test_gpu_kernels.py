@@ -504,13 +504,13 @@ def test_kernels_refuse_what_they_cannot_do():
         ops.gemm_generic(rnd(2, 8), rnd(3, 9))                                       # widths that do not meet
     with pytest.raises(KernelError):
         ops.gemm_generic(rnd(2, 8).half(), rnd(3, 8).half())                         # a dtype nobody wrote
-    H, KV, hd = 2, 1, 272
+    H, KV, hd = 2, 1, 656            # wider than the plain attention's limits (keys of 640, values of 512 numbers)
     q = rnd(1, H * hd)
     kc = torch.zeros(2, KV, 64, hd, device=DEV)
     one = torch.ones(1, dtype=torch.int32, device=DEV)
     with pytest.raises(KernelError) as e:
         ops.attn_decode_generic(q, kc, kc, one.reshape(1, 1), 0 * one, one, 1, H, KV, hd, 1.0, None, 1, torch.zeros_like(q))
-    assert "272" in str(e.value)
+    assert "656" in str(e.value)
 
 
 @pytest.mark.parametrize("m", [1, 3, 8, 9, 16, 17, 40, 64])
