@@ -141,10 +141,31 @@ HYBRID_SIZES = {
 }
 
 
+def _navalorn(width, heads, dim, rot_dim, vdim, kv_rank, q_rank, ff, experts, top, expert_ff, vocab, pairs, **_):
+    mixer = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": kv_rank, "q_rank": q_rank,
+             "scale": (dim + rot_dim) ** -0.5,
+             "rot": {"base": 10000.0, "dims": rot_dim, "scaling": {"factor": 40.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    a = {"type": "latent_attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": ff}}
+    b = {"type": "latent_attention", "mixer": mixer, "mlp": {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": expert_ff}}}
+    return {"architecture": "Navalorn", "width": width, "vocab": vocab, "norm": {"eps": 1e-5}, "layers": [a, b] * pairs}
+
+
+# layer sizes of the kind real models with a latent cache have: two pairs of (latent attention + dense feed-forward, latent
+# attention + scored experts); `kv` and `llama_dim` are the Llama decoder's beside it (same width, heads, feed-forward width)
+LATENT_SIZES = {
+    "w2048": dict(width=2048, heads=16, dim=128, rot_dim=64, vdim=128, kv_rank=512, q_rank=1536, ff=8192, experts=16, top=2,
+                  expert_ff=2048, vocab=32000, pairs=2, kv=4, llama_dim=128),
+    "w4096": dict(width=4096, heads=32, dim=128, rot_dim=64, vdim=128, kv_rank=512, q_rank=1536, ff=14336, experts=16, top=2,
+                  expert_ff=4096, vocab=32000, pairs=2, kv=8, llama_dim=128),
+    "w2048_small": dict(width=2048, heads=32, dim=64, rot_dim=32, vdim=64, kv_rank=256, q_rank=768, ff=8192, experts=32, top=4,
+                        expert_ff=1024, vocab=32000, pairs=2, kv=8, llama_dim=64),
+}
+
+
 def measure_hybrid(args):
-    """`--workload barovik`: prompt and decode throughput of the hybrid decoder at a few real layer sizes (random weights),
-    beside the Llama decoder with the same width, heads, feed-forward width and number of layers; and the device time per
-    kind of operation for one prompt step and one decode step of each.  One JSON line."""
+    """`--workload barovik` / `--workload navalorn`: prompt and decode throughput of that decoder at a few real layer sizes
+    (random weights), beside the Llama decoder with the same width, heads, feed-forward width and number of layers; and the
+    device time per kind of operation for one prompt step and one decode step of each.  One JSON line."""
     import gc
     import numpy as np
     import torch
@@ -222,15 +243,18 @@ def measure_hybrid(args):
         torch.cuda.empty_cache()
         return rec
 
-    names = [n for n in HYBRID_SIZES if not args.sizes or n in args.sizes.split(",")]
+    latent = args.workload == "navalorn"
+    sizes, build, label = (LATENT_SIZES, _navalorn, "navalorn") if latent else (HYBRID_SIZES, _barovik, "barovik")
+    names = [n for n in sizes if not args.sizes or n in args.sizes.split(",")]
     for name in names:
-        z = HYBRID_SIZES[name]
-        hybrid = one(_barovik(**z))
-        out[name] = {"sizes": z, "barovik": hybrid}
+        z = sizes[name]
+        hybrid = one(build(**z))
+        out[name] = {"sizes": z, label: hybrid}
         if not args.skip_points:
-            out[name]["llama_equal_size"] = one(_llama_like(z["width"], z["heads"], z["kv"], z["dim"], z["ff"], z["vocab"], 2 * z["pairs"]))
+            out[name]["llama_equal_size"] = one(_llama_like(z["width"], z["heads"], z["kv"], z["llama_dim"] if latent else z["dim"], z["ff"],
+                                                            z["vocab"], 2 * z["pairs"]))
     clocks.stop()
-    print(json.dumps({"metric": "Barovik beside the Llama decoder at equal layer sizes: prompt and decode tok/s", "impl": "ours", "n_gpus": 1,
+    print(json.dumps({"metric": f"{label.capitalize()} beside the Llama decoder at equal layer sizes: prompt and decode tok/s", "impl": "ours", "n_gpus": 1,
                       "dtype": "bf16", "data": "synthetic: random N(0, 0.02) weights, uniform random token ids", "prompt_len": prompt_len,
                       "decode_batch": batch, "decode_held": held, "steps": steps, "warmup": warm, "peaks": peaks(), "results": out,
                       "clocks": clocks.window(t_begin, time.time())}))
@@ -370,10 +394,10 @@ def main():
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the named configuration (recorded in config)")
     ap.add_argument("--skip-points", action="store_true")
-    ap.add_argument("--workload", default="8b", choices=["8b", "1b", "3b", "barovik"],
-                    help="8b: the headline; 1b, 3b: the baseline's other workloads; barovik: the hybrid decoder beside the Llama "
-                         "decoder at equal layer sizes (--sizes, --batch, --held)")
-    ap.add_argument("--sizes", default="", help="for --workload barovik: which of its sizes to run, with commas (default: all)")
+    ap.add_argument("--workload", default="8b", choices=["8b", "1b", "3b", "barovik", "navalorn"],
+                    help="8b: the headline; 1b, 3b: the baseline's other workloads; barovik, navalorn: the hybrid decoder, or the "
+                         "decoder with a latent cache, beside the Llama decoder at equal layer sizes (--sizes, --batch, --held)")
+    ap.add_argument("--sizes", default="", help="for --workload barovik / navalorn: which of its sizes to run, with commas (default: all)")
     ap.add_argument("--tune", default="", help="overrides of kernel choices, e.g. small_skinny=0,attn_waves=2")
     ap.add_argument("--only", default="", choices=["", "prefill", "decode", "timeline"],
                     help="run one phase alone and print its time (a short program for a launch list under a profiler; no bench "
@@ -396,7 +420,7 @@ def main():
         for kv in filter(None, args.tune.split(",")):
             k, v = kv.split("=")
             _ops.TUNE[k] = type(_ops.TUNE[k])(float(v))
-    if args.workload == "barovik":
+    if args.workload in ("barovik", "navalorn"):
         return measure_hybrid(args)
     if args.workload != "8b":
         return run_workload(args.workload, args)

@@ -157,6 +157,10 @@ int gi_settle(float* x, gi_settle_t settle, const int* rows, int n_rows, int d, 
 // tcgen05 / TMA product for many rows of activations; tile_n is 128 or 256
 int gi_gemm_tc_bf16(void* out, int mode, const void* A, const void* W, int M, int N, int K, long lda, long ldw,
                     long ldo, int tile_n, void* stream);
+#define GI_ACT_RELU2 0x200      // or-ed into GI_TC_STORE_BF16 (gi_gemm_tc_bf16_bias): out = relu(A W^T + bias)^2 as bfloat16
+// gi_gemm_tc_bf16 with `bias` (bfloat16 [N], or null) for the mode GI_TC_STORE_BF16 | GI_ACT_RELU2.
+int gi_gemm_tc_bf16_bias(void* out, int mode, const void* A, const void* W, const void* bias, int M, int N, int K, long lda,
+                         long ldw, long ldo, int tile_n, void* stream);
 // The q/k/v product of a prompt step that rotates and stores in its epilogue (the work of gi_rope_cache_write, the same
 // bits): out [M, N] packed rows of which the queries' columns are written; N = (n_heads + 2 n_kv) * hd, hd 64 or 128.
 int gi_gemm_tc_qkv_rope(void* out, const void* A, const void* W, int M, int N, int K, long lda, long ldw, long ldo,
@@ -220,6 +224,9 @@ int gi_attn_decode_generic_ex2(void* out, long ldo, float* part_o, float* part_m
 // y = (x - mean) / sqrt(var + eps) * w per row, 32-bit statistics; `rows` (optional) picks the rows of x.
 int gi_layernorm(void* out, int out_dtype, const float* x, const void* w, int w_dtype, const int* rows, int n_rows, int d,
                  float eps, void* stream);
+// The same, first adding deferred partial sums to the rows it reads (as gi_rmsnorm_settle does).
+int gi_layernorm_settle(void* out, int out_dtype, float* x, const void* w, int w_dtype, const int* rows, int n_rows, int d,
+                        float eps, gi_settle_t settle, void* stream);
 // out[t, :f] = act(in[t, :f] + bias) (bias optional; act 0: none, 1: relu squared); with `residual` [n_rows, d] also
 // residual[t, :] += res_bias in the same launch.
 int gi_bias_act(void* out, const void* in, int dtype, long ld_in, const void* bias, int w_dtype, int n_rows, int f, int act,
@@ -334,6 +341,10 @@ int gi_moe_gather_rows_scaled(void* out, const void* in, int dtype, long ld_in, 
 int gi_moe_experts_tc(float* out, void* hidden, const void* rows, const void* w_gate_up, long gate_up_stride,
                       const void* w_down, long down_stride, const int* host_offsets, int experts, int width, int f,
                       float* scratch, int* counters, int n_counters, void* stream);
+// The same for ungated experts, hidden = relu(rows W_up^T)^2 with w_up [experts][f][width].
+int gi_moe_experts_tc_ungated(float* out, void* hidden, const void* rows, const void* w_up, long up_stride, const void* w_down,
+                              long down_stride, const int* host_offsets, int experts, int width, int f, float* scratch,
+                              int* counters, int n_counters, void* stream);
 // residual[t, :] += sum_k wts[t, k] * down[inv[t * top + k], :] (k in order; wts null: every weight 1) + sgate[t] *
 // shared[t, :] (if given).
 int gi_moe_combine(float* residual, const float* down, const int* inv, const float* wts, const float* shared,

@@ -69,19 +69,25 @@ attn_latent_mma_kernel(__nv_bfloat16* __restrict__ out, long ldo, float* __restr
     const int page = slot >= 0 ? block_table[(size_t)slot * max_pages + kt / PAGE_TOKENS] : 0;
     const __nv_bfloat16* src0 = kcache + (size_t)page * PAGE_TOKENS * dk;
     __nv_bfloat16* ks = kv_s + (size_t)stage * BKV * ld;
-    for (int idx = tid; idx < BKV * ch; idx += NT) {
-      const int r = idx / ch, c = idx % ch;
-      const int ok = (kt + r <= p_last && c * 8 < dk) ? 16 : 0;      // rows nobody here sees, padding columns: zeros
-      gi::cp_async_16(gi::smem_u32(ks + r * ld + c * 8), src0 + (ok ? (size_t)r * dk + c * 8 : 0), ok);
+    // a warp takes a row at a time, its lanes the row's 16-byte chunks
+    for (int r = warp; r < BKV; r += NT / 32) {
+      const bool seen = kt + r <= p_last;                            // rows nobody here sees, padding columns: zeros
+      for (int c = lane; c < ch; c += 32) {
+        const int ok = (seen && c * 8 < dk) ? 16 : 0;
+        gi::cp_async_16(gi::smem_u32(ks + r * ld + c * 8), src0 + (ok ? (size_t)r * dk + c * 8 : 0), ok);
+      }
     }
   };
 
-  for (int idx = tid; idx < BQ * ch; idx += NT) {
-    const int r = idx / ch, c = idx % ch;
+  // the queries: only the 16-row groups that hold rows are read by anyone
+  for (int r = warp; r < (rows_here + 15) / 16 * 16; r += NT / 32) {
     const int rho = rho0 + r;
-    const int ok = (r < rows_here && c * 8 < dk) ? 16 : 0;
-    const __nv_bfloat16* src = q + (ok ? (size_t)(tok0 + rho / n_heads) * ldq + (size_t)(rho % n_heads) * dk + c * 8 : 0);
-    gi::cp_async_16(gi::smem_u32(q_s + r * ld + c * 8), src, ok);
+    const bool live = r < rows_here;
+    const __nv_bfloat16* src0 = q + (live ? (size_t)(tok0 + rho / n_heads) * ldq + (size_t)(rho % n_heads) * dk : 0);
+    for (int c = lane; c < ch; c += 32) {
+      const int ok = (live && c * 8 < dk) ? 16 : 0;
+      gi::cp_async_16(gi::smem_u32(q_s + r * ld + c * 8), src0 + (ok ? c * 8 : 0), ok);
+    }
   }
   if (tile_lo < tile_hi) issue_kv(tile_lo, 0);
   gi::cp_async_commit();
@@ -225,8 +231,9 @@ attn_latent_mma_kernel(__nv_bfloat16* __restrict__ out, long ldo, float* __restr
   }
 
   // keys mode: the warps' statistics and outputs meet in shared memory (the tiles are not needed any more)
-  float* mo = reinterpret_cast<float*>(smem);                     // [warps][16][NVT * 8]
-  float* mm = mo + (size_t)4 * DSPLIT * 16 * NVT * 8;            // [warps][16] maxima (base 2), then [warps][16] sums
+  constexpr int MO_LD = NVT * 8 + 8;                              // rows 8 floats longer: the warps' stores meet fewer banks twice
+  float* mo = reinterpret_cast<float*>(smem);                     // [warps][16][MO_LD]
+  float* mm = mo + (size_t)4 * DSPLIT * 16 * MO_LD;              // [warps][16] maxima (base 2), then [warps][16] sums
   float* ml = mm + 4 * DSPLIT * 16;
 #pragma unroll
   for (int hh = 0; hh < 2; ++hh) {
@@ -237,8 +244,7 @@ attn_latent_mma_kernel(__nv_bfloat16* __restrict__ out, long ldo, float* __restr
     }
 #pragma unroll
     for (int i = 0; i < NVT; ++i) {
-      mo[((size_t)warp * 16 + row) * (NVT * 8) + i * 8 + 2 * t] = o[i][hh * 2];
-      mo[((size_t)warp * 16 + row) * (NVT * 8) + i * 8 + 2 * t + 1] = o[i][hh * 2 + 1];
+      *reinterpret_cast<float2*>(mo + ((size_t)warp * 16 + row) * MO_LD + i * 8 + 2 * t) = make_float2(o[i][hh * 2], o[i][hh * 2 + 1]);
     }
   }
   __syncthreads();
@@ -256,7 +262,7 @@ attn_latent_mma_kernel(__nv_bfloat16* __restrict__ out, long ldo, float* __restr
         if (mw == -INFINITY) continue;
         const float wgt = exp2f(mw - mx);
         tot += ml[(half * 4 + w) * 16 + row] * wgt;
-        val += mo[((size_t)(half * 4 + w) * 16 + row) * (NVT * 8) + cin] * wgt;
+        val += mo[((size_t)(half * 4 + w) * 16 + row) * MO_LD + cin] * wgt;
       }
     }
     const int rho = rho0 + row;
@@ -279,7 +285,7 @@ int launch(dim3 grid, size_t smem, cudaStream_t s, __nv_bfloat16* out, long ldo,
            const __nv_bfloat16* kc, const int* bt, int max_pages, const int* cu, const int* slots, const int* pos0, const int* lens, int H,
            float scale, int dk, int dv, int hd, int n_splits, int own_tiles) {
   auto kern = attn_latent_mma_kernel<NVT, DSPLIT, KEYS>;
-  if (KEYS) smem = max(smem, (size_t)4 * DSPLIT * 16 * (NVT * 8 + 2) * sizeof(float));
+  if (KEYS) smem = max(smem, (size_t)4 * DSPLIT * 16 * (NVT * 8 + 8 + 2) * sizeof(float));
   static size_t configured[gi::MAX_DEVICES_SEEN] = {0};
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= gi::MAX_DEVICES_SEEN) dev = -1;

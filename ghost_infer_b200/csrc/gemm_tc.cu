@@ -45,7 +45,8 @@ struct TilePlan {
   int wide_cols;     // column tiles of full width
   int narrow;        // width of the column tiles after them (0: none)
   int n_tiles;       // all tiles
-  int act;           // the gated epilogue's activation: 0 silu, 1 gelu (tanh form)
+  int act;           // the gated epilogue's activation: 0 silu, 1 gelu (tanh form); the bfloat16 store's: 2 relu squared
+  const __nv_bfloat16* bias;   // added to the sums before the bfloat16 store's activation (one per output column), or null
 };
 
 // What the q/k/v product's epilogue needs to rotate and store by itself (mode GI_TC_QKV_ROPE): the output's columns are
@@ -309,7 +310,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               uint32_t p[4];
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
-                __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[j + 2 * e]), __uint_as_float(r[j + 2 * e + 1]));
+                float v0 = __uint_as_float(r[j + 2 * e]), v1 = __uint_as_float(r[j + 2 * e + 1]);
+                if (plan.act == 2) {
+                  // an ungated hidden layer: relu(sum + bias)^2 (columns past N are clipped by the store)
+                  const int col = n0 + c * CW + q * 32 + j + 2 * e;
+                  if (plan.bias != nullptr) {
+                    v0 += col < N ? __bfloat162float(plan.bias[col]) : 0.f;
+                    v1 += col + 1 < N ? __bfloat162float(plan.bias[col + 1]) : 0.f;
+                  }
+                  v0 = fmaxf(v0, 0.f);
+                  v1 = fmaxf(v1, 0.f);
+                  v0 *= v0;
+                  v1 *= v1;
+                }
+                __nv_bfloat162 v = __floats2bfloat162_rn(v0, v1);
                 p[e] = *reinterpret_cast<uint32_t*>(&v);
               }
               stage_chunk(stg, row, q * 4 + j / 8, make_uint4(p[0], p[1], p[2], p[3]));
@@ -473,9 +487,17 @@ int launch_mode(int mode, const CUtensorMap& ma, const CUtensorMap& mw, const CU
 
 extern "C" int gi_gemm_tc_bf16(void* out, int mode, const void* A, const void* W, int M, int N, int K, long lda, long ldw,
                                long ldo, int tile_n, void* stream) {
-  const int act = (mode & GI_ACT_GELU) ? 1 : 0;
+  return gi_gemm_tc_bf16_bias(out, mode, A, W, nullptr, M, N, K, lda, ldw, ldo, tile_n, stream);
+}
+
+extern "C" int gi_gemm_tc_bf16_bias(void* out, int mode, const void* A, const void* W, const void* bias, int M, int N, int K,
+                                    long lda, long ldw, long ldo, int tile_n, void* stream) {
+  const bool relu2 = (mode & GI_ACT_RELU2) != 0;
+  const int act = relu2 ? 2 : ((mode & GI_ACT_GELU) ? 1 : 0);
   mode &= 0xff;
-  if (act && mode != GI_TC_SWIGLU) return gi::fail(GI_ERR_ARG, "tensor-core product: an activation without a gated mode");
+  if (relu2 ? mode != GI_TC_STORE_BF16 : (act && mode != GI_TC_SWIGLU))
+    return gi::fail(GI_ERR_ARG, "tensor-core product: an activation without the mode that applies it");
+  if (bias != nullptr && !relu2) return gi::fail(GI_ERR_ARG, "tensor-core product: a bias goes with the squared relu's store");
   if (M <= 0 || N <= 0) return GI_OK;
   if (K <= 0 || K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0)
     return gi::fail(GI_ERR_UNSUPPORTED, "tensor-core product: K (%d) and the row strides (%ld, %ld) must be multiples of 8", K, lda, ldw);
@@ -499,6 +521,7 @@ extern "C" int gi_gemm_tc_bf16(void* out, int mode, const void* A, const void* W
   const int gran = mode == GI_TC_SWIGLU ? 128 : (mode == GI_TC_STORE_BF16 ? 64 : 32);
   TilePlan plan = g_tail_tiles ? plan_tiles(M, N, tile_n, gran, sm_count()) : plan_tiles(M, N, tile_n, gran, 0);
   plan.act = act;
+  plan.bias = (const __nv_bfloat16*)bias;
   CUtensorMap mw2 = mw;
   if (plan.narrow > 0) {
     rc = gi::tensor_map_2d(&mw2, W, N, K, ldw, plan.narrow);

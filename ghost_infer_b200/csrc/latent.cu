@@ -70,6 +70,67 @@ layernorm_kernel(TO* __restrict__ out, const float* x, const TW* __restrict__ w,
   }
 }
 
+// The same with a row in registers as float4 (widths that are multiples of 4, up to 4096, rows on 16-byte boundaries), and,
+// SETTLE, first adding the partial sums a deferred product left for the rows it reads (written back to x unless `rows`
+// selects: then x is left as it is and must not be read again).
+__device__ __forceinline__ float4 pending_sum4(const gi_settle_t& st, int m, int f) {
+  const gi_settle_span sp = gi_span_of(st, f);
+  if (sp.c_first == sp.c_last) return make_float4(0.f, 0.f, 0.f, 0.f);     // one block had the whole tile and added it itself
+  return gi_sum_pieces4(st, sp, m, f);
+}
+
+template <typename TO, typename TW, bool SETTLE>
+__global__ void __launch_bounds__(256)
+layernorm_vec_kernel(TO* __restrict__ out, float* x, const TW* __restrict__ w, const int* rows, int d, float eps, gi_settle_t st) {
+  __shared__ float scratch[33];
+  gi::pdl_prologue();
+  const int r = blockIdx.x;
+  const int m = rows ? rows[r] : r;
+  float4* xr = reinterpret_cast<float4*>(x + (size_t)m * d);
+  TO* o = out + (size_t)r * d;
+  const int n4 = d / 4;
+  float4 v[4];
+  float s = 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int i = threadIdx.x + j * 256;
+    v[j] = i < n4 ? xr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    if (SETTLE && i < n4) {
+      const float4 p = pending_sum4(st, m, 4 * i);
+      v[j].x += p.x;
+      v[j].y += p.y;
+      v[j].z += p.z;
+      v[j].w += p.w;
+      if (rows == nullptr) xr[i] = v[j];
+    }
+    s += (v[j].x + v[j].y) + (v[j].z + v[j].w);
+  }
+  const float mean = gi::block_sum(s, scratch) / (float)d;
+  float q = 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int i = threadIdx.x + j * 256;
+    if (i < n4) {
+      const float a = v[j].x - mean, b = v[j].y - mean, c = v[j].z - mean, e = v[j].w - mean;
+      q = fmaf(a, a, q);
+      q = fmaf(b, b, q);
+      q = fmaf(c, c, q);
+      q = fmaf(e, e, q);
+    }
+  }
+  const float rstd = 1.0f / sqrtf(gi::block_sum(q, scratch) / (float)d + eps);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int i = threadIdx.x + j * 256;
+    if (i < n4) {
+      gi::stf(o + 4 * i, (v[j].x - mean) * rstd * gi::ldf(w + 4 * i));
+      gi::stf(o + 4 * i + 1, (v[j].y - mean) * rstd * gi::ldf(w + 4 * i + 1));
+      gi::stf(o + 4 * i + 2, (v[j].z - mean) * rstd * gi::ldf(w + 4 * i + 2));
+      gi::stf(o + 4 * i + 3, (v[j].w - mean) * rstd * gi::ldf(w + 4 * i + 3));
+    }
+  }
+}
+
 // ---- bias and activation -------------------------------------------------------------------------------------------
 // act 0: none; 1: relu(z)^2.
 template <typename T, typename TW>
@@ -217,14 +278,17 @@ bmm_heads_kernel(TO* __restrict__ out, long ldo, long ohs, const TA* A, long lda
 // ---- the same on tensor cores: bfloat16 in and out, W_h stored [N][K] row-major (kstride 1) -------------------------------
 // A block takes 64 rows x 64 columns of one head: four warps of 16 rows each, `mma.sync m16n8k16` with 32-bit sums; the
 // operands of a 32-wide slice of K go through shared memory (rows padded to 40 values, so that the fragments' loads
-// meet no bank twice).  Edges are filled with zeros and not stored.
+// meet no bank twice).  Edges are filled with zeros and not stored.  VEC: every row of both operands starts on a 16-byte
+// boundary and K is a multiple of 8, so the slices arrive by `cp.async`, 16 bytes a copy, the next slice under way while
+// this one is multiplied; else element by element, one slice at a time.
 constexpr int TK = 32, TLD = TK + 8;
 
+template <bool VEC>
 __global__ void __launch_bounds__(128)
 bmm_heads_mma_kernel(__nv_bfloat16* __restrict__ out, long ldo, long ohs, const __nv_bfloat16* A, long lda, long ahs,
                      const __nv_bfloat16* __restrict__ W, long whs, long ldw, int M, int N, int K) {
-  __shared__ __align__(16) __nv_bfloat16 As[64 * TLD];
-  __shared__ __align__(16) __nv_bfloat16 Ws[64 * TLD];
+  __shared__ __align__(16) __nv_bfloat16 As[2][64 * TLD];
+  __shared__ __align__(16) __nv_bfloat16 Ws[2][64 * TLD];
   gi::pdl_prologue();
   const int h = blockIdx.z, m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
   const __nv_bfloat16* Ah = A + (size_t)h * ahs;
@@ -236,45 +300,55 @@ bmm_heads_mma_kernel(__nv_bfloat16* __restrict__ out, long ldo, long ohs, const 
 #pragma unroll
     for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
   const __nv_bfloat16 zero = __float2bfloat16_rn(0.f);
-  for (int k0 = 0; k0 < K; k0 += TK) {
-    // 64 rows x 32 values of each operand: 2048 values, 16 per thread, in pairs
-    for (int idx = tid; idx < 64 * (TK / 2); idx += 128) {
-      const int rr = idx / (TK / 2), kk = 2 * (idx % (TK / 2)), k = k0 + kk;
-      __nv_bfloat16 a0 = zero, a1 = zero, w0 = zero, w1 = zero;
-      if (m0 + rr < M) {
-        const __nv_bfloat16* p = Ah + (size_t)(m0 + rr) * lda + k;
-        if (k < K) a0 = p[0];
-        if (k + 1 < K) a1 = p[1];
+  const int n_slices = (K + TK - 1) / TK;
+
+  auto fill = [&](int slice, int stage) {
+    const int k0 = slice * TK;
+    if (VEC) {
+      // 64 rows x 4 chunks of 8 values per operand: two chunks of each per thread
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int idx = tid + i * 128;
+        const int rr = idx >> 2, kk = (idx & 3) * 8, k = k0 + kk;
+        const int oka = (m0 + rr < M && k < K) ? 16 : 0, okw = (n0 + rr < N && k < K) ? 16 : 0;
+        gi::cp_async_16(gi::smem_u32(&As[stage][rr * TLD + kk]), Ah + (oka ? (size_t)(m0 + rr) * lda + k : 0), oka);
+        gi::cp_async_16(gi::smem_u32(&Ws[stage][rr * TLD + kk]), Wh + (okw ? (size_t)(n0 + rr) * ldw + k : 0), okw);
       }
-      if (n0 + rr < N) {
-        const __nv_bfloat16* p = Wh + (size_t)(n0 + rr) * ldw + k;
-        if (k < K) w0 = p[0];
-        if (k + 1 < K) w1 = p[1];
+    } else {
+      for (int idx = tid; idx < 64 * TK; idx += 128) {
+        const int rr = idx / TK, kk = idx % TK, k = k0 + kk;
+        As[stage][rr * TLD + kk] = (m0 + rr < M && k < K) ? Ah[(size_t)(m0 + rr) * lda + k] : zero;
+        Ws[stage][rr * TLD + kk] = (n0 + rr < N && k < K) ? Wh[(size_t)(n0 + rr) * ldw + k] : zero;
       }
-      As[rr * TLD + kk] = a0;
-      As[rr * TLD + kk + 1] = a1;
-      Ws[rr * TLD + kk] = w0;
-      Ws[rr * TLD + kk + 1] = w1;
+    }
+  };
+
+  fill(0, 0);
+  if (VEC) gi::cp_async_commit();
+  for (int sl = 0; sl < n_slices; ++sl) {
+    const int stage = VEC ? (sl & 1) : 0;
+    if (VEC) {
+      if (sl + 1 < n_slices) fill(sl + 1, stage ^ 1);
+      gi::cp_async_commit();
+      gi::cp_async_wait<1>();
     }
     __syncthreads();
 #pragma unroll
     for (int ks = 0; ks < TK; ks += 16) {
       uint32_t a[4];
-      const __nv_bfloat16* ar = As + (warp * 16 + g) * TLD + ks + 2 * c;
+      const __nv_bfloat16* ar = &As[stage][(warp * 16 + g) * TLD + ks + 2 * c];
       a[0] = *reinterpret_cast<const uint32_t*>(ar);
       a[1] = *reinterpret_cast<const uint32_t*>(ar + 8 * TLD);
       a[2] = *reinterpret_cast<const uint32_t*>(ar + 8);
       a[3] = *reinterpret_cast<const uint32_t*>(ar + 8 * TLD + 8);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        const __nv_bfloat16* wr = Ws + (j * 8 + g) * TLD + ks + 2 * c;
-        uint32_t b[2];
-        b[0] = *reinterpret_cast<const uint32_t*>(wr);
-        b[1] = *reinterpret_cast<const uint32_t*>(wr + 8);
-        gi::mma_16816(acc[j], a, b[0], b[1]);
+        const __nv_bfloat16* wr = &Ws[stage][(j * 8 + g) * TLD + ks + 2 * c];
+        gi::mma_16816(acc[j], a, *reinterpret_cast<const uint32_t*>(wr), *reinterpret_cast<const uint32_t*>(wr + 8));
       }
     }
     __syncthreads();
+    if (!VEC && sl + 1 < n_slices) fill(sl + 1, 0);
   }
   const int r_lo = m0 + warp * 16 + g, r_hi = r_lo + 8;
 #pragma unroll
@@ -291,13 +365,101 @@ bmm_heads_mma_kernel(__nv_bfloat16* __restrict__ out, long ldo, long ohs, const 
   }
 }
 
+// ---- the same for a step of few rows (one-token steps): bound by the bytes of the heads' matrices ------------------------
+// grid (column tiles of 32, heads); a block stages up to 8 rows' numbers for its head in shared memory and streams 32 rows of
+// the head's matrix past them, 16 bytes per lane per load, four columns in flight; a warp takes 8 columns, its lanes cut K
+// between them and their sums meet in a fixed order.  bfloat16, K a multiple of 8, rows on 16-byte boundaries.
+constexpr int GV_ROWS = 8, GV_COLS = 32;
+
+__global__ void __launch_bounds__(128)
+bmm_heads_gemv_kernel(__nv_bfloat16* __restrict__ out, long ldo, long ohs, const __nv_bfloat16* A, long lda, long ahs,
+                      const __nv_bfloat16* __restrict__ W, long whs, long ldw, int M, int N, int K) {
+  extern __shared__ __align__(16) unsigned char gv_smem[];
+  __nv_bfloat16* As = reinterpret_cast<__nv_bfloat16*>(gv_smem);      // [GV_ROWS][K]
+  gi::pdl_prologue();
+  const int h = blockIdx.y;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const __nv_bfloat16* Ah = A + (size_t)h * ahs;
+  const __nv_bfloat16* Wh = W + (size_t)h * whs;
+  const int n_base = blockIdx.x * GV_COLS + warp * 8;
+  for (int r0 = 0; r0 < M; r0 += GV_ROWS) {
+    const int rows = min(GV_ROWS, M - r0);
+    __syncthreads();
+    for (int idx = tid; idx < rows * (K / 8); idx += 128) {
+      const int r = idx / (K / 8), ch = idx % (K / 8);
+      *reinterpret_cast<uint4*>(As + (size_t)r * K + ch * 8) = *reinterpret_cast<const uint4*>(Ah + (size_t)(r0 + r) * lda + ch * 8);
+    }
+    __syncthreads();
+    for (int j0 = 0; j0 < 8; j0 += 4) {
+      if (n_base + j0 >= N) break;                      // the same for the whole warp
+      const __nv_bfloat16* wp[4];
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) wp[jj] = Wh + (size_t)min(n_base + j0 + jj, N - 1) * ldw;     // past the end: repeated, not stored
+      float acc[4][GV_ROWS];
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj)
+#pragma unroll
+        for (int r = 0; r < GV_ROWS; ++r) acc[jj][r] = 0.f;
+      for (int k = lane * 8; k < K; k += 256) {
+        uint4 wv[4];
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) wv[jj] = *reinterpret_cast<const uint4*>(wp[jj] + k);
+#pragma unroll
+        for (int r = 0; r < GV_ROWS; ++r) {
+          if (r < rows) {
+            const uint4 av = *reinterpret_cast<const uint4*>(As + (size_t)r * K + k);
+            const uint32_t aw[4] = {av.x, av.y, av.z, av.w};
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) {
+              const uint32_t ww[4] = {wv[jj].x, wv[jj].y, wv[jj].z, wv[jj].w};
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                acc[jj][r] = fmaf(__uint_as_float(aw[i] << 16), __uint_as_float(ww[i] << 16), acc[jj][r]);
+                acc[jj][r] = fmaf(__uint_as_float(aw[i] & 0xffff0000u), __uint_as_float(ww[i] & 0xffff0000u), acc[jj][r]);
+              }
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) {
+        const int n = n_base + j0 + jj;
+#pragma unroll
+        for (int r = 0; r < GV_ROWS; ++r) {
+          if (r >= rows) break;
+          const float v = gi::warp_sum(acc[jj][r]);
+          if (lane == 0 && n < N) out[(size_t)(r0 + r) * ldo + (size_t)h * ohs + n] = __float2bfloat16_rn(v);
+        }
+      }
+    }
+  }
+}
+
 }  // namespace
 
 extern "C" int gi_layernorm(void* out, int out_dtype, const float* x, const void* w, int w_dtype, const int* rows, int n_rows,
                             int d, float eps, void* stream) {
+  gi_settle_t none = {nullptr, nullptr, nullptr, nullptr, 0};
+  return gi_layernorm_settle(out, out_dtype, const_cast<float*>(x), w, w_dtype, rows, n_rows, d, eps, none, stream);
+}
+
+extern "C" int gi_layernorm_settle(void* out, int out_dtype, float* x, const void* w, int w_dtype, const int* rows, int n_rows,
+                                   int d, float eps, gi_settle_t settle, void* stream) {
   if (n_rows <= 0) return GI_OK;
   if (d <= 0) return gi::fail(GI_ERR_ARG, "layernorm: bad width %d", d);
   cudaError_t e = cudaSuccess;
+  const bool vec = d % 4 == 0 && d <= 4096 && !((uintptr_t)x & 15);
+  if (settle.partials != nullptr && !vec)
+    return gi::fail(GI_ERR_UNSUPPORTED, "layernorm: settling partial sums needs rows of a multiple of 4 and at most 4096 values");
+  if (vec) {
+    if (settle.partials != nullptr)
+      GI_DISPATCH_DTYPE(out_dtype, TO, GI_DISPATCH_DTYPE(w_dtype, TW,
+          e = gi::launch(layernorm_vec_kernel<TO, TW, true>, dim3(n_rows), dim3(256), 0, (cudaStream_t)stream, (TO*)out, x, (const TW*)w, rows, d, eps, settle)));
+    else
+      GI_DISPATCH_DTYPE(out_dtype, TO, GI_DISPATCH_DTYPE(w_dtype, TW,
+          e = gi::launch(layernorm_vec_kernel<TO, TW, false>, dim3(n_rows), dim3(256), 0, (cudaStream_t)stream, (TO*)out, x, (const TW*)w, rows, d, eps, settle)));
+    return gi::check(e, "layernorm");
+  }
   GI_DISPATCH_DTYPE(out_dtype, TO, GI_DISPATCH_DTYPE(w_dtype, TW,
       e = gi::launch(layernorm_kernel<TO, TW>, dim3(n_rows), dim3(256), 0, (cudaStream_t)stream, (TO*)out, x, (const TW*)w, rows, d, eps)));
   return gi::check(e, "layernorm");
@@ -306,7 +468,8 @@ extern "C" int gi_layernorm(void* out, int out_dtype, const float* x, const void
 extern "C" int gi_bias_act(void* out, const void* in, int dtype, long ld_in, const void* bias, int w_dtype, int n_rows, int f,
                            int act, float* residual, const void* res_bias, int d, void* stream) {
   if (n_rows <= 0) return GI_OK;
-  if (f <= 0 || (act != 0 && act != 1)) return gi::fail(GI_ERR_ARG, "bias_act: bad width %d or activation %d", f, act);
+  if (f < 0 || (f == 0 && residual == nullptr) || (act != 0 && act != 1))
+    return gi::fail(GI_ERR_ARG, "bias_act: bad width %d or activation %d", f, act);
   if ((residual != nullptr) != (res_bias != nullptr) || (residual != nullptr && d <= 0))
     return gi::fail(GI_ERR_ARG, "bias_act: a bias for the residual rows needs both the rows and the bias");
   const size_t total_act = (size_t)n_rows * f;
@@ -359,8 +522,28 @@ extern "C" int gi_bmm_heads(void* out, long ldo, long ohs, const void* a, long l
   cudaError_t e = cudaSuccess;
   if (tensor_cores && dtype == GI_BF16 && w_dtype == GI_BF16 && kstride == 1 && lda % 2 == 0 && ahs % 2 == 0 && ldw % 2 == 0 &&
       whs % 2 == 0 && !(((uintptr_t)a | (uintptr_t)w) & 3)) {
-    e = gi::launch(bmm_heads_mma_kernel, grid, dim3(128), 0, (cudaStream_t)stream, (__nv_bfloat16*)out, ldo, ohs,
-                   (const __nv_bfloat16*)a, lda, ahs, (const __nv_bfloat16*)w, whs, ldw, M, N, K);
+    const bool vec = K % 8 == 0 && lda % 8 == 0 && ahs % 8 == 0 && ldw % 8 == 0 && whs % 8 == 0 && !(((uintptr_t)a | (uintptr_t)w) & 15);
+    if (vec && M <= 32 && (size_t)GV_ROWS * K * 2 <= 96 * 1024) {
+      // few rows: the matrices are streamed once
+      const size_t smem = (size_t)GV_ROWS * K * 2;
+      static size_t configured[gi::MAX_DEVICES_SEEN] = {0};
+      int dev = -1;
+      if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= gi::MAX_DEVICES_SEEN) dev = -1;
+      if (smem > 48 * 1024 && (dev < 0 || configured[dev] < smem)) {
+        e = cudaFuncSetAttribute(bmm_heads_gemv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return gi::fail(GI_ERR_CUDA, "per-head product: %s", cudaGetErrorString(e));
+        if (dev >= 0) configured[dev] = smem;
+      }
+      e = gi::launch(bmm_heads_gemv_kernel, dim3((N + GV_COLS - 1) / GV_COLS, heads), dim3(128), smem, (cudaStream_t)stream,
+                     (__nv_bfloat16*)out, ldo, ohs, (const __nv_bfloat16*)a, lda, ahs, (const __nv_bfloat16*)w, whs, ldw, M, N, K);
+      return gi::check(e, "per-head product (few rows)");
+    }
+    if (vec)
+      e = gi::launch(bmm_heads_mma_kernel<true>, grid, dim3(128), 0, (cudaStream_t)stream, (__nv_bfloat16*)out, ldo, ohs,
+                     (const __nv_bfloat16*)a, lda, ahs, (const __nv_bfloat16*)w, whs, ldw, M, N, K);
+    else
+      e = gi::launch(bmm_heads_mma_kernel<false>, grid, dim3(128), 0, (cudaStream_t)stream, (__nv_bfloat16*)out, ldo, ohs,
+                     (const __nv_bfloat16*)a, lda, ahs, (const __nv_bfloat16*)w, whs, ldw, M, N, K);
     return gi::check(e, "per-head product");
   }
   GI_DISPATCH_DTYPE(dtype, T, GI_DISPATCH_DTYPE(w_dtype, TW,

@@ -554,9 +554,29 @@ extern "C" int gi_moe_gather_rows_scaled(void* out, const void* in, int dtype, l
 // every expert with rows, hidden = act(rows W_gate^T) * (rows W_up^T) (gate and up rows interleaved in blocks of 8) and
 // out = hidden W_down^T as float, over the expert's stretch of the sorted rows.  Stretches of up to 64 rows take the
 // streamed product, longer ones the tiled one.  One call per layer, so that the host's share is the launches alone.
+static int experts_tc(float* out, void* hidden, const void* rows, const void* w_gate_up, long gate_up_stride,
+                      const void* w_down, long down_stride, const int* host_offsets, int experts, int width, int f,
+                      float* scratch, int* counters, int n_counters, void* stream, bool ungated);
+
 extern "C" int gi_moe_experts_tc(float* out, void* hidden, const void* rows, const void* w_gate_up, long gate_up_stride,
                                  const void* w_down, long down_stride, const int* host_offsets, int experts, int width, int f,
                                  float* scratch, int* counters, int n_counters, void* stream) {
+  return experts_tc(out, hidden, rows, w_gate_up, gate_up_stride, w_down, down_stride, host_offsets, experts, width, f, scratch,
+                    counters, n_counters, stream, false);
+}
+
+// The same for ungated experts: hidden = relu(rows W_up^T)^2 (w_up [experts][f][width]), the activation in the first
+// product's epilogue; every stretch takes the tiled product.
+extern "C" int gi_moe_experts_tc_ungated(float* out, void* hidden, const void* rows, const void* w_up, long up_stride,
+                                         const void* w_down, long down_stride, const int* host_offsets, int experts, int width,
+                                         int f, float* scratch, int* counters, int n_counters, void* stream) {
+  return experts_tc(out, hidden, rows, w_up, up_stride, w_down, down_stride, host_offsets, experts, width, f, scratch, counters,
+                    n_counters, stream, true);
+}
+
+static int experts_tc(float* out, void* hidden, const void* rows, const void* w_gate_up, long gate_up_stride,
+                      const void* w_down, long down_stride, const int* host_offsets, int experts, int width, int f,
+                      float* scratch, int* counters, int n_counters, void* stream, bool ungated) {
   if (experts <= 0 || width <= 0 || f <= 0 || f % 8 != 0 || width % 8 != 0)
     return gi::fail(GI_ERR_UNSUPPORTED, "experts on tensor cores: width %d and hidden width %d must be multiples of 8", width, f);
   const __nv_bfloat16* a = (const __nv_bfloat16*)rows;
@@ -571,7 +591,9 @@ extern "C" int gi_moe_experts_tc(float* out, void* hidden, const void* rows, con
   static bool made[gi::MAX_DEVICES_SEEN] = {false};
   int dev = -1;
   bool many = false;
-  for (int e = 0; e < experts; ++e) many = many || host_offsets[e + 1] - host_offsets[e] > 64;
+  const int small = ungated ? 0 : 64;      // stretches of up to this many rows take the streamed product (gated experts only)
+  const int up_rows = ungated ? f : 2 * f;
+  for (int e = 0; e < experts; ++e) many = many || host_offsets[e + 1] - host_offsets[e] > small;
   cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
   cudaStreamIsCapturing(main_stream, &capturing);
   bool fan = many && capturing == cudaStreamCaptureStatusNone && cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < gi::MAX_DEVICES_SEEN;
@@ -589,14 +611,15 @@ extern "C" int gi_moe_experts_tc(float* out, void* hidden, const void* rows, con
   int turn = 0;
   for (int e = 0; e < experts; ++e) {
     const int lo = host_offsets[e], m = host_offsets[e + 1] - lo;
-    if (m <= 64) continue;
+    if (m <= small) continue;
     const __nv_bfloat16* wgu = (const __nv_bfloat16*)w_gate_up + (size_t)e * gate_up_stride;
     const __nv_bfloat16* wd = (const __nv_bfloat16*)w_down + (size_t)e * down_stride;
     cudaStream_t s = fan ? side[dev][turn++ % SIDE] : main_stream;
     // narrower tiles where wide ones would leave most SMs without one
     const int row_tiles = (m + 127) / 128;
-    const int tile_up = row_tiles * ((2 * f + 255) / 256) < 64 ? 128 : 256, tile_down = row_tiles * ((width + 255) / 256) < 64 ? 128 : 256;
-    int rc = gi_gemm_tc_bf16(h + (size_t)lo * f, GI_TC_SWIGLU, a + (size_t)lo * width, wgu, m, 2 * f, width, width, width, f, tile_up, s);
+    const int tile_up = row_tiles * ((up_rows + 255) / 256) < 64 ? 128 : 256, tile_down = row_tiles * ((width + 255) / 256) < 64 ? 128 : 256;
+    int rc = gi_gemm_tc_bf16(h + (size_t)lo * f, ungated ? (GI_TC_STORE_BF16 | GI_ACT_RELU2) : GI_TC_SWIGLU, a + (size_t)lo * width, wgu, m,
+                             up_rows, width, width, width, f, tile_up, s);
     if (rc == GI_OK)
       rc = gi_gemm_tc_bf16(out + (size_t)lo * width, GI_TC_STORE_F32, h + (size_t)lo * f, wd, m, width, f, f, f, width, tile_down, s);
     if (rc != GI_OK) return rc;
@@ -610,7 +633,7 @@ extern "C" int gi_moe_experts_tc(float* out, void* hidden, const void* rows, con
   }
   for (int e = 0; e < experts; ++e) {
     const int lo = host_offsets[e], m = host_offsets[e + 1] - lo;
-    if (m <= 0 || m > 64) continue;
+    if (m <= 0 || m > small) continue;
     const __nv_bfloat16* wgu = (const __nv_bfloat16*)w_gate_up + (size_t)e * gate_up_stride;
     const __nv_bfloat16* wd = (const __nv_bfloat16*)w_down + (size_t)e * down_stride;
     int rc = gi_gemm_stream_bf16(h + (size_t)lo * f, GI_SKINNY_SWIGLU, a + (size_t)lo * width, wgu, scratch, counters, n_counters, m,

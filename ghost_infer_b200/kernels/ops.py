@@ -93,12 +93,15 @@ def _bind():
         "gi_attn_prefill_generic_ex2": [P, L, P, L, I, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, F, P, I, L, P],
         "gi_attn_decode_generic_ex2": [P, L, P, P, P, L, I, P, P, P, I, P, P, I, I, I, I, F, I, I, I, I, F, P, I, L, P],
         "gi_layernorm": [P, I, P, P, I, P, I, I, F, P],
+        "gi_layernorm_settle": [P, I, P, P, I, P, I, I, F, SettleT, P],
         "gi_bias_act": [P, P, I, L, P, I, I, I, I, P, P, I, P],
         "gi_latent_prepare": [P, P, I, L, P, P, I, F, P, I, P, P, P, I, P, I, I, I, I, I, P],
         "gi_latent_query_rot": [P, L, P, L, I, P, I, I, I, I, I, I, P],
         "gi_bmm_heads": [P, L, L, P, L, L, I, P, I, L, L, L, I, I, I, I, I, P],
         "gi_rope_table_scaled": [P, P, P, I, I, F, P],
         "gi_attn_latent_tc": [P, L, P, P, P, L, P, P, I, P, P, P, P, I, I, I, I, I, F, I, I, P],
+        "gi_gemm_tc_bf16_bias": [P, I, P, P, P, I, I, I, L, L, L, I, P],
+        "gi_moe_experts_tc_ungated": [P, P, P, P, L, P, L, P, I, I, I, P, P, I, P],
     }
     for name, argtypes in sigs.items():
         fn = getattr(lib, name)
@@ -1590,6 +1593,31 @@ def moe_experts_by_expert(rows: torch.Tensor, w_gate_up: torch.Tensor, w_down: t
     return out
 
 
+def moe_experts_by_expert_ungated(rows: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, host_offsets) -> torch.Tensor:
+    """`moe_experts_by_expert` for ungated experts: W_down,e relu(W_up,e row)^2 over every expert's stretch of the sorted
+    rows, float32 [entries, width]; the squared relu rides in the first product's epilogue.  bfloat16."""
+    lib = _bind()
+    _cuda(rows, "sorted rows")
+    experts, f, width = w_up.shape
+    entries = rows.shape[0]
+    if (rows.dtype != torch.bfloat16 or w_up.dtype != torch.bfloat16 or w_down.dtype != torch.bfloat16 or not rows.is_contiguous()
+            or rows.shape[1] != width or tuple(w_down.shape) != (experts, width, f) or not w_up.is_contiguous()
+            or not w_down.is_contiguous() or f % 8 or width % 8):
+        raise KernelError("experts on tensor cores take contiguous bfloat16 rows and weights of fitting sizes, multiples of 8")
+    if len(host_offsets) != experts + 1 or host_offsets[0] != 0 or host_offsets[-1] != entries or any(
+            b < a for a, b in zip(host_offsets, host_offsets[1:])):
+        raise KernelError("the experts' offsets do not cover the rows")
+    hidden = torch.empty((entries, f), dtype=torch.bfloat16, device=rows.device)
+    out = torch.empty((entries, width), dtype=torch.float32, device=rows.device)
+    scratch, counters = _stream_buffers(rows.device)
+    offs = (c_int * (experts + 1))(*[int(x) for x in host_offsets])
+    n_live = sum(1 for a, b in zip(host_offsets, host_offsets[1:]) if b > a)
+    _check(lib, lib.gi_moe_experts_tc_ungated(out.data_ptr(), hidden.data_ptr(), rows.data_ptr(), w_up.data_ptr(), w_up.stride(0),
+                                              w_down.data_ptr(), w_down.stride(0), offs, experts, width, f, scratch.data_ptr(),
+                                              counters.data_ptr(), counters.numel(), _stream()), 2 * n_live)
+    return out
+
+
 def moe_combine(residual: torch.Tensor, down: torch.Tensor, inv: torch.Tensor, wts: Optional[torch.Tensor],
                 shared: Optional[torch.Tensor] = None, shared_gate: Optional[torch.Tensor] = None) -> None:
     """residual[t] += sum_k wts[t, k] * down[inv[t, k]] (+ shared_gate[t] * shared[t]); `wts` None: every weight 1."""
@@ -1613,7 +1641,7 @@ def layernorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torc
               rows: Optional[torch.Tensor] = None) -> torch.Tensor:
     """(x - mean) / sqrt(var + eps) * weight per row of the float32 matrix `x` (statistics in 32-bit)."""
     lib = _bind()
-    _cuda(x, "layernorm input")
+    _cuda(x, "layernorm input", settles=True)
     if x.dtype != torch.float32 or x.dim() != 2 or not x.is_contiguous():
         raise KernelError("layernorm input must be a contiguous float32 [rows, width] matrix")
     d = x.shape[1]
@@ -1621,6 +1649,17 @@ def layernorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torc
         raise KernelError(f"layernorm weight has {weight.numel()} values, the rows are {d} wide")
     n = x.shape[0] if rows is None else rows.numel()
     out = torch.empty((n, d), dtype=out_dtype, device=x.device)
+    pending = _take_pending(x)
+    if pending is not None and (pending[1] or d % 4 != 0 or d > 4096 or x.data_ptr() % 16 != 0):
+        x.__dict__["_gi_pending"] = pending         # not sums this kernel can add: the plain way
+        settle(x)
+        pending = None
+    if pending is not None:
+        # a deferred product left partial sums for this stream: they are added while the rows are read anyway
+        _check(lib, lib.gi_layernorm_settle(out.data_ptr(), _dt(out, "layernorm output"), x.data_ptr(), weight.data_ptr(),
+                                            _dt(weight, "layernorm weight"), _i32(rows, "rows"), n, d, float(eps), pending[0],
+                                            _stream()))
+        return out
     _check(lib, lib.gi_layernorm(out.data_ptr(), _dt(out, "layernorm output"), x.data_ptr(), weight.data_ptr(),
                                  _dt(weight, "layernorm weight"), _i32(rows, "rows"), n, d, float(eps), _stream()))
     return out
@@ -1652,6 +1691,38 @@ def bias_act(rows: torch.Tensor, bias: Optional[torch.Tensor], act: Optional[str
                                 residual.data_ptr() if residual is not None else None,
                                 residual_bias.data_ptr() if residual is not None else None, d, _stream()))
     return out
+
+
+ACT_RELU2 = 0x200       # or-ed into SKINNY_STORE_BF16 for the tensor-core product: relu(sum + bias)^2
+
+
+def linear_act(h: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], act: str = "relu2") -> torch.Tensor:
+    """act(h W^T + bias) in h's type (`act` "relu2": relu squared).  A prompt step's product on the tensor cores adds the
+    bias and applies the activation in its epilogue; other products are followed by `bias_act`."""
+    if act != "relu2":
+        raise KernelError(f"unknown activation \"{act}\" (relu2)")
+    if (tc_ok(h, w) and h.shape[0] > SKINNY_MAX_ROWS and w.shape[0] % 8 == 0
+            and (bias is None or (bias.dtype == torch.bfloat16 and bias.is_contiguous() and bias.numel() == w.shape[0]))):
+        lib = _bind()
+        _cuda(h, "activations")
+        m, k = h.shape
+        n = w.shape[0]
+        out = torch.empty((m, n), dtype=torch.bfloat16, device=h.device)
+        _check(lib, lib.gi_gemm_tc_bf16_bias(out.data_ptr(), SKINNY_STORE_BF16 | ACT_RELU2, h.data_ptr(), w.data_ptr(),
+                                             bias.data_ptr() if bias is not None else None, m, n, k, _rows(h, "activations"),
+                                             _rows(w, "weights"), n, int(TC_TILE_N), _stream()))
+        return out
+    return bias_act(linear(h, w, out_dtype=h.dtype), bias, act)
+
+
+def add_row_bias(residual: torch.Tensor, bias: torch.Tensor) -> None:
+    """residual[t, :] += bias for every row of the float32 matrix `residual`."""
+    lib = _bind()
+    _cuda(residual, "residual stream")
+    n, d = residual.shape
+    if residual.dtype != torch.float32 or not residual.is_contiguous() or bias.numel() != d or not bias.is_contiguous():
+        raise KernelError("the stream's rows must be contiguous float32 with a bias of their width")
+    _check(lib, lib.gi_bias_act(None, None, F32, 0, None, _dt(bias, "bias"), n, 0, 0, residual.data_ptr(), bias.data_ptr(), d, _stream()))
 
 
 def latent_prepare(rows: torch.Tensor, w_query_norm: Optional[torch.Tensor], w_latent_norm: torch.Tensor, eps: float,
@@ -1727,7 +1798,8 @@ def attn_latent_decode_plan(n_seqs: int, max_kv_len: int, sm_count: int, n_heads
     if attn_latent_tc_ok(dtype, rank, rot_dim):
         tiles = (max_kv_len + 63) // 64
         blocks = n_seqs * ((n_heads + 63) // 64)
-        return "tensor cores", max(1, min(tiles, (sm_count + blocks - 1) // blocks)), 0
+        # one block per SM (the tiles' ring fills its shared memory): as many slices as make one round of blocks
+        return "tensor cores", max(1, min(tiles, sm_count // max(blocks, 1))), 0
     tiles = (max_kv_len + 31) // 32
     return "plain", max(1, (tiles + OWN_LENGTH_TILES - 1) // OWN_LENGTH_TILES), OWN_LENGTH_TILES
 

@@ -102,8 +102,14 @@ class Mlp(FeedForward):
 
     def forward(self, h, residual, step) -> None:
         with ops.bucket("ffn matmul"):
-            up = linear(h, self.w_up, out_dtype=self.rt.dtype)
             if self.bias:
                 ops.settle(residual)         # the rows get the output's bias from a plain kernel, which adds no partial sums
-            act = ops.bias_act(up, self.b_up, self.activation, residual if self.bias else None, self.b_down)
+            if step.is_decode or not h.is_cuda or h.dtype != torch.bfloat16:
+                # bias and activation as a step of its own, which also puts the output's bias onto the stream
+                up = linear(h, self.w_up, out_dtype=self.rt.dtype)
+                act = ops.bias_act(up, self.b_up, self.activation, residual if self.bias else None, self.b_down)
+            else:
+                act = ops.linear_act(h, self.w_up, self.b_up, self.activation)      # in the product's epilogue where it can
+                if self.bias:
+                    ops.add_row_bias(residual, self.b_down)
             linear(act, self.w_down, out=residual, accumulate=True)

@@ -182,13 +182,7 @@ class ScoredExperts(FeedForward):
             if self._by_expert(h, step):
                 # enough rows per expert: the host reads the experts' offsets back (one wait) and every expert's stretch
                 # goes through the products the dense layers use
-                offs = offsets.cpu().tolist()
-                down = torch.empty((rows.shape[0], self.hidden), dtype=torch.float32, device=h.device)
-                for e in range(self.experts):
-                    lo, hi = offs[e], offs[e + 1]
-                    if hi > lo:
-                        up = linear(rows[lo:hi], self.w_up[e], out_dtype=h.dtype)
-                        linear(ops.bias_act(up, None, self.activation), self.w_down[e], out=down[lo:hi])
+                down = ops.moe_experts_by_expert_ungated(rows, self.w_up, self.w_down, offsets.cpu().tolist())
             else:
                 hidden = ops.moe_rows_product(rows, self.w_up, offsets, act=self.activation)
                 down = ops.moe_rows_product(hidden, self.w_down, offsets)

@@ -42,7 +42,7 @@ class RmsNorm(Norm):
 
 @register("norm", "layernorm")
 class LayerNorm(Norm):
-    settles_pending = False     # whoever calls it settles a deferred product's partial sums first
+    settles_pending = True      # its kernel adds partial sums a deferred product left for the rows it reads
 
     def __init__(self, params, prefix=""):
         super().__init__(params, prefix)

@@ -154,20 +154,22 @@ def test_latent_rows(dtype, rq, r, dr, rot):
 
 
 @pytest.mark.parametrize("dtype,tc", [("float32", False), ("bfloat16", False), ("bfloat16", True)])
-@pytest.mark.parametrize("M,H,N,K", [(5, 3, 40, 24), (130, 2, 72, 100), (64, 5, 8, 16), (1, 16, 128, 64)])
-def test_one_product_per_head(dtype, tc, M, H, N, K):
+@pytest.mark.parametrize("M,H,N,K,pad", [(5, 3, 40, 24, 6), (130, 2, 72, 100, 6), (64, 5, 8, 16, 6), (1, 16, 128, 64, 6),
+                                         (5, 3, 40, 24, 8), (1, 16, 128, 64, 8), (19, 2, 33, 512, 0),       # few rows, 16-byte rows
+                                         (130, 2, 72, 104, 8), (40, 3, 100, 256, 8), (300, 2, 512, 128, 64)])  # many rows, 16-byte rows
+def test_one_product_per_head(dtype, tc, M, H, N, K, pad):
     dt = DT[dtype]
     g = torch.Generator(device=DEV).manual_seed(M + N)
-    a = torch.randn((M, H * (K + 6)), device=DEV, generator=g).to(dt)        # a head's numbers start every K + 6
+    a = torch.randn((M, H * (K + pad)), device=DEV, generator=g).to(dt)      # a head's numbers start every K + pad
     w = (torch.randn((H, N, K), device=DEV, generator=g) * 0.2).to(dt)
     out = torch.full((M, H * (N + 2)), 7.0, dtype=dt, device=DEV)
     old = ops.TUNE["bmm_heads_tc"]
     ops.TUNE["bmm_heads_tc"] = tc
     try:
-        ops.bmm_heads(out, N + 2, a, K + 6, w, N, K)
+        ops.bmm_heads(out, N + 2, a, K + pad, w, N, K)
     finally:
         ops.TUNE["bmm_heads_tc"] = old
-    ref = torch.einsum("mhk,hnk->mhn", a.double().view(M, H, K + 6)[:, :, :K], w.double())
+    ref = torch.einsum("mhk,hnk->mhn", a.double().view(M, H, K + pad)[:, :, :K], w.double())
     got = out.double().view(M, H, N + 2)
     torch.testing.assert_close(got[:, :, :N], ref, **tol(dtype))
     assert float((got[:, :, N:] - 7.0).abs().max()) == 0.0          # nothing past a head's columns is touched
@@ -295,3 +297,36 @@ def test_scored_experts_pieces(dtype, tokens, experts, top):
     ops.moe_combine(res, down, inv, None)
     want = before + down.double()[inv.long()].view(tokens, top, width).sum(1)
     torch.testing.assert_close(res.double(), want, rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("rows,n,k,with_bias", [(70, 136, 96, True), (300, 264, 128, False), (65, 8, 8, True)])
+def test_squared_relu_in_the_product_epilogue(rows, n, k, with_bias):
+    g = torch.Generator(device=DEV).manual_seed(rows)
+    h = torch.randn((rows, k), device=DEV, generator=g).to(torch.bfloat16)
+    w = (torch.randn((n, k), device=DEV, generator=g) * 0.2).to(torch.bfloat16)
+    b = torch.randn((n,), device=DEV, generator=g).to(torch.bfloat16) if with_bias else None
+    got = ops.linear_act(h, w, b, "relu2")
+    ref = torch.relu(h.double() @ w.double().T + (b.double() if with_bias else 0.0)) ** 2
+    torch.testing.assert_close(got.double(), ref, rtol=2e-2, atol=2e-2)
+    few = ops.linear_act(h[:9], w, b, "relu2")                     # few rows: product, then bias and activation
+    torch.testing.assert_close(few.double(), ref[:9], rtol=2e-2, atol=2e-2)
+    res = torch.randn((rows, 12), device=DEV, generator=g)
+    before = res.clone()
+    rb = torch.randn((12,), device=DEV, generator=g).to(torch.bfloat16)
+    ops.add_row_bias(res, rb)
+    torch.testing.assert_close(res.double(), before.double() + rb.double(), rtol=1e-6, atol=1e-6)
+
+
+def test_ungated_experts_stretch_by_stretch():
+    experts, width, ff = 5, 64, 40
+    g = torch.Generator(device=DEV).manual_seed(1)
+    counts = [130, 0, 7, 64, 200]
+    offs = [0] + np.cumsum(counts).tolist()
+    rows = torch.randn((offs[-1], width), device=DEV, generator=g).to(torch.bfloat16)
+    w_up = (torch.randn((experts, ff, width), device=DEV, generator=g) * 0.2).to(torch.bfloat16)
+    w_down = (torch.randn((experts, width, ff), device=DEV, generator=g) * 0.2).to(torch.bfloat16)
+    got = ops.moe_experts_by_expert_ungated(rows, w_up, w_down, offs)
+    for e in range(experts):
+        lo, hi = offs[e], offs[e + 1]
+        hid = (torch.relu(rows[lo:hi].double() @ w_up[e].double().T) ** 2).to(torch.bfloat16).double()
+        torch.testing.assert_close(got[lo:hi].double(), hid @ w_down[e].double().T, rtol=2e-2, atol=2e-2)
