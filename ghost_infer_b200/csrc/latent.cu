@@ -198,20 +198,92 @@ latent_prepare_kernel(T* __restrict__ cq, const T* in, long ld, const TW* __rest
   for (int i = 2 * half + threadIdx.x; i < dr; i += 128) dst[r + i] = kr[i];
 }
 
-template <typename T>
-__global__ void latent_query_rot_kernel(T* qa, long ldqa, const T* q, long ldq, const float2* table, int half, int dn, int dr,
-                                        int r) {
+// The same with 16-byte accesses and the row kept in registers: bfloat16, every part a multiple of 8 numbers wide, rows on
+// 16-byte boundaries, at most 4096 numbers in the two latents together.  A thread holds up to two chunks of 8 numbers; both
+// sums of squares go through the block at once.
+template <typename TW>
+__global__ void __launch_bounds__(256)
+latent_prepare_vec_kernel(__nv_bfloat16* __restrict__ cq, const __nv_bfloat16* in, long ld, const TW* __restrict__ wq,
+                          const TW* __restrict__ wc, float eps, const float2* table, int half, const int* positions,
+                          const int* slots, const int* block_table, int max_pages, __nv_bfloat16* kcache, int rq, int r, int dr,
+                          int write_cache) {
+  __shared__ float scratch[33];
   gi::pdl_prologue();
-  const int t = blockIdx.x, h = blockIdx.y;
-  const T* src = q + (size_t)t * ldq + (size_t)h * (dn + dr) + dn;
-  T* dst = qa + (size_t)t * ldqa + (size_t)h * (r + dr) + r;
-  for (int i = threadIdx.x; i < half; i += blockDim.x) {
-    float a, b;
-    gi::rotate_pair(gi::ldf(src + 2 * i), gi::ldf(src + 2 * i + 1), table[(size_t)t * half + i], &a, &b);
-    gi::stf(dst + 2 * i, a);
-    gi::stf(dst + 2 * i + 1, b);
+  const int t = blockIdx.x;
+  const __nv_bfloat16* row = in + (size_t)t * ld;
+  const int nq = rq / 8, nc = r / 8;               // chunks of the two latents
+  float v[2][8];
+  float ssq = 0.f, ssc = 0.f;
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const int ci = threadIdx.x + j * 256;
+    if (ci < nq + nc) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(row + ci * 8);
+      const uint32_t w4[4] = {raw.x, raw.y, raw.z, raw.w};
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        v[j][2 * i] = __uint_as_float(w4[i] << 16);
+        v[j][2 * i + 1] = __uint_as_float(w4[i] & 0xffff0000u);
+        ss = fmaf(v[j][2 * i], v[j][2 * i], ss);
+        ss = fmaf(v[j][2 * i + 1], v[j][2 * i + 1], ss);
+      }
+      if (ci < nq) ssq += ss; else ssc += ss;
+    }
   }
-  for (int i = 2 * half + threadIdx.x; i < dr; i += blockDim.x) dst[i] = src[i];
+  const float rsq = rq > 0 ? 1.0f / sqrtf(gi::block_sum(ssq, scratch) / (float)rq + eps) : 0.f;
+  const float rsc = 1.0f / sqrtf(gi::block_sum(ssc, scratch) / (float)r + eps);
+  __nv_bfloat16* dst = nullptr;
+  if (write_cache) {
+    const int slot = slots[t];
+    const int pos = max(positions[t], 0);
+    const int page = slot >= 0 ? block_table[(size_t)slot * max_pages + pos / PAGE_TOKENS] : 0;
+    dst = kcache + ((size_t)page * PAGE_TOKENS + pos % PAGE_TOKENS) * (size_t)(r + dr);
+  }
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const int ci = threadIdx.x + j * 256;
+    if (ci >= nq + nc) continue;
+    const bool is_q = ci < nq;
+    if (!is_q && !write_cache) continue;
+    const TW* w = is_q ? wq + ci * 8 : wc + (ci - nq) * 8;
+    const float rs = is_q ? rsq : rsc;
+    uint32_t p[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) p[i] = gi::pack_bf16(v[j][2 * i] * rs * gi::ldf(w + 2 * i), v[j][2 * i + 1] * rs * gi::ldf(w + 2 * i + 1));
+    __nv_bfloat16* o = is_q ? cq + (size_t)t * rq + ci * 8 : dst + (ci - nq) * 8;
+    *reinterpret_cast<uint4*>(o) = make_uint4(p[0], p[1], p[2], p[3]);
+  }
+  if (!write_cache) return;
+  const __nv_bfloat16* kr = row + rq + r;
+  for (int i = threadIdx.x; i < half; i += 256) {
+    float a, b;
+    gi::rotate_pair(gi::ldf(kr + 2 * i), gi::ldf(kr + 2 * i + 1), table[(size_t)t * half + i], &a, &b);
+    gi::stf(dst + r + 2 * i, a);
+    gi::stf(dst + r + 2 * i + 1, b);
+  }
+  for (int i = 2 * half + threadIdx.x; i < dr; i += 256) dst[r + i] = kr[i];
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+latent_query_rot_kernel(T* qa, long ldqa, const T* q, long ldq, const float2* table, int half, int n_heads, int dn, int dr, int r) {
+  gi::pdl_prologue();
+  const int t = blockIdx.x;
+  const int per = dr - half;                       // work items of a head: `half` pairs, then dr - 2 half numbers that pass
+  for (int idx = threadIdx.x; idx < n_heads * per; idx += 256) {
+    const int h = idx / per, i = idx % per;
+    const T* src = q + (size_t)t * ldq + (size_t)h * (dn + dr) + dn;
+    T* dst = qa + (size_t)t * ldqa + (size_t)h * (r + dr) + r;
+    if (i < half) {
+      float a, b;
+      gi::rotate_pair(gi::ldf(src + 2 * i), gi::ldf(src + 2 * i + 1), table[(size_t)t * half + i], &a, &b);
+      gi::stf(dst + 2 * i, a);
+      gi::stf(dst + 2 * i + 1, b);
+    } else {
+      dst[half + i] = src[half + i];
+    }
+  }
 }
 
 // ---- one small product per head, CUDA cores ------------------------------------------------------------------------
@@ -366,10 +438,10 @@ bmm_heads_mma_kernel(__nv_bfloat16* __restrict__ out, long ldo, long ohs, const 
 }
 
 // ---- the same for a step of few rows (one-token steps): bound by the bytes of the heads' matrices ------------------------
-// grid (column tiles of 32, heads); a block stages up to 8 rows' numbers for its head in shared memory and streams 32 rows of
-// the head's matrix past them, 16 bytes per lane per load, four columns in flight; a warp takes 8 columns, its lanes cut K
+// grid (column tiles of 16, heads); a block stages up to 8 rows' numbers for its head in shared memory and streams 16 rows of
+// the head's matrix past them, 16 bytes per lane per load, four columns in flight; a warp takes 4 columns, its lanes cut K
 // between them and their sums meet in a fixed order.  bfloat16, K a multiple of 8, rows on 16-byte boundaries.
-constexpr int GV_ROWS = 8, GV_COLS = 32;
+constexpr int GV_ROWS = 8, GV_COLS = 16;      // a warp takes 4 columns
 
 __global__ void __launch_bounds__(128)
 bmm_heads_gemv_kernel(__nv_bfloat16* __restrict__ out, long ldo, long ohs, const __nv_bfloat16* A, long lda, long ahs,
@@ -381,7 +453,7 @@ bmm_heads_gemv_kernel(__nv_bfloat16* __restrict__ out, long ldo, long ohs, const
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const __nv_bfloat16* Ah = A + (size_t)h * ahs;
   const __nv_bfloat16* Wh = W + (size_t)h * whs;
-  const int n_base = blockIdx.x * GV_COLS + warp * 8;
+  const int n_base = blockIdx.x * GV_COLS + warp * 4;
   for (int r0 = 0; r0 < M; r0 += GV_ROWS) {
     const int rows = min(GV_ROWS, M - r0);
     __syncthreads();
@@ -390,7 +462,7 @@ bmm_heads_gemv_kernel(__nv_bfloat16* __restrict__ out, long ldo, long ohs, const
       *reinterpret_cast<uint4*>(As + (size_t)r * K + ch * 8) = *reinterpret_cast<const uint4*>(Ah + (size_t)(r0 + r) * lda + ch * 8);
     }
     __syncthreads();
-    for (int j0 = 0; j0 < 8; j0 += 4) {
+    for (int j0 = 0; j0 < 4; j0 += 4) {
       if (n_base + j0 >= N) break;                      // the same for the whole warp
       const __nv_bfloat16* wp[4];
 #pragma unroll
@@ -492,6 +564,14 @@ extern "C" int gi_latent_prepare(void* cq, const void* in, int dtype, long ld, c
   if (rot > 0 && table == nullptr) return gi::fail(GI_ERR_ARG, "latent rows: no table of angles");
   if (write_cache && (!kcache || !block_table || !slots || !positions)) return gi::fail(GI_ERR_ARG, "latent rows: cache write without a cache");
   cudaError_t e = cudaSuccess;
+  if (dtype == GI_BF16 && rq % 8 == 0 && r % 8 == 0 && dr % 8 == 0 && ld % 8 == 0 && rq + r <= 4096 &&
+      !(((uintptr_t)in | (uintptr_t)cq | (uintptr_t)kcache) & 15) && !(((uintptr_t)wq | (uintptr_t)wc) & 15)) {
+    GI_DISPATCH_DTYPE(w_dtype, TW,
+        e = gi::launch(latent_prepare_vec_kernel<TW>, dim3(n_tokens), dim3(256), 0, (cudaStream_t)stream, (__nv_bfloat16*)cq,
+                       (const __nv_bfloat16*)in, ld, (const TW*)wq, (const TW*)wc, eps, (const float2*)table, rot / 2, positions, slots,
+                       block_table, max_pages, (__nv_bfloat16*)kcache, rq, r, dr, write_cache));
+    return gi::check(e, "latent rows");
+  }
   GI_DISPATCH_DTYPE(dtype, T, GI_DISPATCH_DTYPE(w_dtype, TW,
       e = gi::launch(latent_prepare_kernel<T, TW>, dim3(n_tokens), dim3(128), 0, (cudaStream_t)stream, (T*)cq, (const T*)in, ld,
                      (const TW*)wq, (const TW*)wc, eps, (const float2*)table, rot / 2, positions, slots, block_table, max_pages,
@@ -507,8 +587,8 @@ extern "C" int gi_latent_query_rot(void* qa, long ldqa, const void* q, long ldq,
   if (rot > 0 && table == nullptr) return gi::fail(GI_ERR_ARG, "latent queries: no table of angles");
   cudaError_t e = cudaSuccess;
   GI_DISPATCH_DTYPE(dtype, T,
-      e = gi::launch(latent_query_rot_kernel<T>, dim3(n_tokens, n_heads), dim3(32), 0, (cudaStream_t)stream, (T*)qa, ldqa,
-                     (const T*)q, ldq, (const float2*)table, rot / 2, dn, dr, r));
+      e = gi::launch(latent_query_rot_kernel<T>, dim3(n_tokens), dim3(256), 0, (cudaStream_t)stream, (T*)qa, ldqa,
+                     (const T*)q, ldq, (const float2*)table, rot / 2, n_heads, dn, dr, r));
   return gi::check(e, "latent queries");
 }
 
