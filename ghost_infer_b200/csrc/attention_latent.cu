@@ -47,7 +47,8 @@ attn_latent_mma_kernel(__nv_bfloat16* __restrict__ out, long ldo, float* __restr
   const int qlen = decode ? 1 : cu_seqlens[b + 1] - tok0;
   const int pos0 = decode ? seq_lens[b] - 1 : seq_pos0[b];
   const int R = qlen * n_heads;                     // (token, head) rows of this sequence's step
-  const int rho0 = blockIdx.x * BQ;
+  // the latest rows of a sequence see the most keys: their blocks start first
+  const int rho0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * BQ;
   if (rho0 >= R) return;
   const int slot = seq_slots[b];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -124,6 +125,39 @@ attn_latent_mma_kernel(__nv_bfloat16* __restrict__ out, long ldo, float* __restr
       for (int nt = 0; nt < NS; ++nt)
 #pragma unroll
         for (int c = 0; c < 4; ++c) s[nt][c] = 0.f;
+      if (KEYS) {
+        // 16 keys a warp: two chains of products (even and odd slices of the columns) instead of one, added at the end
+        float s2[NS][4];
+#pragma unroll
+        for (int nt = 0; nt < NS; ++nt)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) s2[nt][c] = 0.f;
+        const uint32_t q_at = gi::smem_u32(q_s + ((lane & 7) + ((lane >> 3) & 1) * 8) * ld + (lane >> 4) * 8);
+        const uint32_t k_at = gi::smem_u32(ks_ + (key0 + (lane >> 4) * 8 + (lane & 7)) * ld + ((lane >> 3) & 1) * 8);
+        const int steps = hd / 16;
+        for (int kp = 0; kp + 1 < steps; kp += 2) {
+          uint32_t qa_[4], qb_[4], ka_[4], kb_[4];
+          gi::ldmatrix_x4(qa_, q_at + kp * 32);
+          gi::ldmatrix_x4(ka_, k_at + kp * 32);
+          gi::ldmatrix_x4(qb_, q_at + kp * 32 + 32);
+          gi::ldmatrix_x4(kb_, k_at + kp * 32 + 32);
+          gi::mma_16816(s[0], qa_, ka_[0], ka_[1]);
+          gi::mma_16816(s[1], qa_, ka_[2], ka_[3]);
+          gi::mma_16816(s2[0], qb_, kb_[0], kb_[1]);
+          gi::mma_16816(s2[1], qb_, kb_[2], kb_[3]);
+        }
+        if (steps & 1) {
+          uint32_t qa_[4], ka_[4];
+          gi::ldmatrix_x4(qa_, q_at + (steps - 1) * 32);
+          gi::ldmatrix_x4(ka_, k_at + (steps - 1) * 32);
+          gi::mma_16816(s[0], qa_, ka_[0], ka_[1]);
+          gi::mma_16816(s[1], qa_, ka_[2], ka_[3]);
+        }
+#pragma unroll
+        for (int nt = 0; nt < NS; ++nt)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) s[nt][c] += s2[nt][c];
+      } else {
       for (int kp = 0; kp < hd / 16; ++kp) {
         uint32_t qf[4];
         gi::ldmatrix_x4(qf, gi::smem_u32(q_s + (wr * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ld + (kp * 2 + (lane >> 4)) * 8));
@@ -135,6 +169,7 @@ attn_latent_mma_kernel(__nv_bfloat16* __restrict__ out, long ldo, float* __restr
           gi::mma_16816(s[n2 * 2], qf, kb[0], kb[1]);
           gi::mma_16816(s[n2 * 2 + 1], qf, kb[2], kb[3]);
         }
+      }
       }
       float tmax[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -248,33 +283,40 @@ attn_latent_mma_kernel(__nv_bfloat16* __restrict__ out, long ldo, float* __restr
     }
   }
   __syncthreads();
-  for (int idx = tid; idx < rows_here * dv; idx += NT) {
-    const int row = idx / dv, col = idx % dv;
-    const int half = col / (NVT * 8), cin = col % (NVT * 8);
-    float mx = -INFINITY;
+  // sixteen threads a row: a row's weights are worked out once, then its columns are walked
+  {
+    const int row = tid >> 4, c0 = tid & 15;
+    if (row < rows_here) {                       // NT / 16 >= 8 rows a pass; rows_here <= 16
+      for (int rr = row; rr < rows_here; rr += NT / 16) {
+        const int rho = rho0 + rr;
+        const int tokl = rho / n_heads, head = rho % n_heads;
+        const size_t pi = ((size_t)b * n_heads + head) * n_splits + sp;
+        for (int half = 0; half < DSPLIT; ++half) {
+          float mx = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) mx = fmaxf(mx, mm[(half * 4 + w) * 16 + row]);
-    float tot = 0.f, val = 0.f;
-    if (mx != -INFINITY) {
+          for (int w = 0; w < 4; ++w) mx = fmaxf(mx, mm[(half * 4 + w) * 16 + rr]);
+          float wgt[4], tot = 0.f;
 #pragma unroll
-      for (int w = 0; w < 4; ++w) {
-        const float mw = mm[(half * 4 + w) * 16 + row];
-        if (mw == -INFINITY) continue;
-        const float wgt = exp2f(mw - mx);
-        tot += ml[(half * 4 + w) * 16 + row] * wgt;
-        val += mo[((size_t)(half * 4 + w) * 16 + row) * MO_LD + cin] * wgt;
-      }
-    }
-    const int rho = rho0 + row;
-    const int tokl = rho / n_heads, head = rho % n_heads;
-    if (n_splits == 1) {
-      out[(size_t)(tok0 + tokl) * ldo + (size_t)head * dv + col] = __float2bfloat16_rn(tot > 0.f ? val / tot : 0.f);
-    } else {
-      const size_t pi = ((size_t)b * n_heads + head) * n_splits + sp;
-      part_o[pi * dv + col] = val;
-      if (col == 0) {
-        part_ml[pi * 2] = mx == -INFINITY ? -INFINITY : mx * LN2;
-        part_ml[pi * 2 + 1] = tot;
+          for (int w = 0; w < 4; ++w) {
+            const float mw = mm[(half * 4 + w) * 16 + rr];
+            wgt[w] = (mx == -INFINITY || mw == -INFINITY) ? 0.f : exp2f(mw - mx);
+            tot += ml[(half * 4 + w) * 16 + rr] * wgt[w];
+          }
+          const float inv = tot > 0.f ? 1.0f / tot : 0.f;
+          const int col_end = min(dv, (half + 1) * NVT * 8);
+          for (int col = half * NVT * 8 + c0; col < col_end; col += 16) {
+            const int cin = col - half * NVT * 8;
+            float val = 0.f;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) val += mo[((size_t)(half * 4 + w) * 16 + rr) * MO_LD + cin] * wgt[w];
+            if (n_splits == 1) out[(size_t)(tok0 + tokl) * ldo + (size_t)head * dv + col] = __float2bfloat16_rn(val * inv);
+            else part_o[pi * dv + col] = val;
+          }
+          if (n_splits > 1 && half == 0 && c0 == 0) {
+            part_ml[pi * 2] = mx == -INFINITY ? -INFINITY : mx * LN2;
+            part_ml[pi * 2 + 1] = tot;
+          }
+        }
       }
     }
   }
