@@ -4,7 +4,8 @@
     python -m ghost_infer_b200.kernels.microbench --kernel attn_decode --batch 8 --context 2048
 
 Kernels: gemm_stream, gemm_skinny (decode products), gemm_tc (prefill product), attn_decode, attn_prefill (mma.sync),
-attn_prefill_t5 (tcgen05),
+attn_prefill_t5 (tcgen05), attn_latent_decode, attn_latent_prefill (attention over one shared latent row per position:
+--heads, --rank, --rot-dim),
 rmsnorm, rope, sample.  Operands rotate through enough different buffers to exceed the L2 cache, so a bytes
 figure is a DRAM figure.  The same command under `ncu --clock-control none -k regex:<kernel> -c 3` profiles exactly these launches.
 The reference times whole runs only (`bench`, src/main.rs:1241-1285) and, per operation, wall-clock buckets
@@ -58,6 +59,8 @@ def main() -> int:
     ap.add_argument("--heads", type=int, default=32)
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--rank", type=int, default=512, help="attn_latent_*: numbers of the latent (the values' width)")
+    ap.add_argument("--rot-dim", type=int, default=64, help="attn_latent_*: numbers of the rotated key part behind the latent")
     ap.add_argument("--splits", type=int, default=0)
     ap.add_argument("--own-tiles", type=int, default=0, help="attn_decode: slices of that many tiles of each sequence's own span")
     ap.add_argument("--tile-keys", type=int, default=0, help="attn_decode: 16 or 32 keys per tile (default: the engine's)")
@@ -140,6 +143,42 @@ def main() -> int:
                        1, args.iters, args.warmup)
             flops = 2.0 * B * H * hd * S * (S + 1)
             out.update(shape=[B, S, H, KV, hd], us=round(us, 2), tflops=round(flops / us / 1e6, 1),
+                       frac_tensor=round(flops / us / 1e6 / tflops, 3))
+    elif args.kernel in ("attn_latent_decode", "attn_latent_prefill"):
+        from types import SimpleNamespace
+        from ..cache.sequence_cache import LayerMemory
+        B, S, H, r, dr = args.batch, args.context, args.heads, args.rank, args.rot_dim
+        dk = r + dr
+        pages_per = (S + 63) // 64
+        decode = args.kernel == "attn_latent_decode"
+        n_sets = max(2, L2_BYTES * 2 // (B * pages_per * 64 * dk * 2) + 1) if decode else 1
+        kc = torch.randn(n_sets * B * pages_per + 1, 1, 64, dk, device=dev, dtype=bf) * 0.5
+        tables = [(torch.arange(B * pages_per, dtype=torch.int32, device=dev).reshape(B, pages_per) + 1 + s * B * pages_per) for s in range(n_sets)]
+        mems = [LayerMemory(kc, None, t, None, True, None) for t in tables]
+        slots = torch.arange(B, dtype=torch.int32, device=dev)
+        sms = torch.cuda.get_device_properties(0).multi_processor_count
+        scale = dk ** -0.5
+        if decode:
+            step = SimpleNamespace(n_seqs=B, n_tokens=B, max_q_len=1, max_kv_len=S, is_decode=True, seq_slots=slots,
+                                   seq_lens=torch.full((B,), S, dtype=torch.int32, device=dev), sm_count=sms)
+            qa = torch.randn(B, H * dk, device=dev, dtype=bf) * 0.5
+            o = torch.empty(B, H * r, device=dev, dtype=bf)
+            plan = ops.attn_latent_decode_plan(B, S, sms, H, r, dr, bf)
+            if args.splits:
+                plan = (plan[0], args.splits, 0)
+            us = _time(lambda i: ops.attention_latent(qa, mems[i], step, H, r, dr, scale, o, plan=plan), n_sets, args.iters, args.warmup)
+            nbytes = B * S * dk * 2
+            out.update(shape=[B, S, H, r, dr], plan=list(plan), us=round(us, 2), gbs=round(nbytes / us / 1e3, 1),
+                       frac_hbm=round(nbytes / us / 1e3 / hbm, 3))
+        else:
+            step = SimpleNamespace(n_seqs=B, n_tokens=B * S, max_q_len=S, max_kv_len=S, is_decode=False, seq_slots=slots,
+                                   cu_seqlens=torch.arange(B + 1, dtype=torch.int32, device=dev) * S,
+                                   seq_pos0=torch.zeros(B, dtype=torch.int32, device=dev), sm_count=sms)
+            qa = torch.randn(B * S, H * dk, device=dev, dtype=bf) * 0.5
+            o = torch.empty(B * S, H * r, device=dev, dtype=bf)
+            us = _time(lambda i: ops.attention_latent(qa, mems[0], step, H, r, dr, scale, o), 1, args.iters, args.warmup)
+            flops = 2.0 * B * H * (dk + r) * S * (S + 1) / 2
+            out.update(shape=[B, S, H, r, dr], us=round(us, 2), tflops=round(flops / us / 1e6, 1),
                        frac_tensor=round(flops / us / 1e6 / tflops, 3))
     elif args.kernel == "rmsnorm":
         x = torch.randn(args.m, args.k, device=dev)
